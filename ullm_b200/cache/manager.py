@@ -67,12 +67,41 @@ class LayerCache:
     group: "object | None"  # engine.batch.GroupStep of this execution's group
     writes: bool
     state: torch.Tensor | None  # [slots, *shape] or None
+    aux: "LayerCache | None" = None  # the execution's second cache (`Mixer.aux_cache_need`), if it asked for one
 
 
 def plan_groups(needs) -> tuple[list[GroupInfo], list[tuple[int, int] | None]]:
-    """needs: per schedule entry (CacheNeed | None, StateNeed | None, cache_of).
+    """needs: per schedule entry (CacheNeed | None, StateNeed | None, cache_of[, second CacheNeed | None]).
     Returns the groups and, per entry, (group, index inside the group) of the
     cache it uses (its own or the one it reads), or None."""
+    groups, where, _aux = plan_groups_with_aux(needs)
+    return groups, where
+
+
+def plan_groups_with_aux(needs):
+    """`plan_groups`, and per entry the place of its second cache (or None) as a third result."""
+    needs = [tuple(n) for n in needs]
+    aux_needs = [n[3] if len(n) > 3 else None for n in needs]
+    groups, where = _plan_main([n[:3] for n in needs])
+    where_aux: list[tuple[int, int] | None] = []
+    for i, need in enumerate(aux_needs):
+        if need is None:
+            where_aux.append(None)
+            continue
+        if need.window is not None and need.every > 1:
+            raise ValueError(f"schedule entry {i}: a cache with one entry per {need.every} tokens keeps all of them")
+        for g, info in enumerate(groups):
+            if info.need == need:
+                info.executions.append(-1 - i)  # (a second cache: no execution of its own stands behind it)
+                where_aux.append((g, len(info.executions) - 1))
+                break
+        else:
+            groups.append(GroupInfo(need, [-1 - i]))
+            where_aux.append((len(groups) - 1, 0))
+    return groups, where, where_aux
+
+
+def _plan_main(needs):
     groups: list[GroupInfo] = []
     where: list[tuple[int, int] | None] = []
     needs = list(needs)
@@ -91,7 +120,8 @@ def plan_groups(needs) -> tuple[list[GroupInfo], list[tuple[int, int] | None]]:
         have = kept[cache_of]
         window = None if (have.window is None or need.window is None) else max(have.window, need.window)
         kept[cache_of] = CacheNeed(have.num_kv_heads, have.head_dim, window, have.value_dim,
-                                   0 if window is None else max(have.keep_first, need.keep_first))
+                                   0 if window is None else max(have.keep_first, need.keep_first),
+                                   have.values_in_keys, have.every)
     for i, (need, _state, cache_of) in enumerate(needs):
         if need is None:
             where.append(None)
@@ -131,10 +161,17 @@ class CacheManager:
         self.device = torch.device(device) if device is not None else None
         self.dtype = dtype
         self.needs = list(needs)
-        self.groups, self.where = plan_groups(self.needs)
-        self.allocators = [PageAllocator(num_pages) for _ in self.groups]
+        self.groups, self.where, self.where_aux = plan_groups_with_aux(self.needs)
+        for g in self.groups:
+            if g.need.every < 1 or (g.need.every > 1 and g.need.window is not None):
+                raise ValueError("a cache with one entry per several tokens keeps all its entries (no window)")
+        # a group with one entry per n tokens needs a page per n pages of tokens, and one more per request for
+        # the page each is filling
+        self.group_pages = [num_pages if g.need.every == 1 else -(-num_pages // g.need.every) + max_requests
+                            for g in self.groups]
+        self.allocators = [PageAllocator(n) for n in self.group_pages]
         self.slots = SlotAllocator(max_requests)
-        has_state = any(s is not None for _, s, _ in self.needs)
+        has_state = any(n[1] is not None for n in self.needs)
         only_full = len(self.groups) == 1 and self.groups[0].need.window is None
         self.tree = PrefixTree(page_size) if (enable_prefix_cache and only_full and not has_state) else None
         if enable_prefix_cache and self.tree is None:
@@ -157,8 +194,8 @@ class CacheManager:
         self._flush_next = 0
         if self.device is not None:
             pin = self.device.type == "cuda"
-            for g in self.groups:
-                shape = (len(g.executions), num_pages, page_size, g.need.num_kv_heads, g.need.head_dim)
+            for g, pages_g in zip(self.groups, self.group_pages):
+                shape = (len(g.executions), pages_g, page_size, g.need.num_kv_heads, g.need.head_dim)
                 k = torch.empty(shape, dtype=dtype, device=self.device)
                 v = torch.empty(shape[:-1] + (g.need.v_dim,), dtype=dtype, device=self.device)
                 if poison:
@@ -176,16 +213,17 @@ class CacheManager:
             n = max(1, len(self.groups)) * max_requests * max_pages_per_request
             self._flush_ring = [torch.empty(n, dtype=torch.int32, pin_memory=pin) for _ in range(4)]
             self._flush_events = [torch.cuda.Event() if pin else None for _ in range(4)]
-            for i, (_need, state, _c) in enumerate(self.needs):
+            for i, n in enumerate(self.needs):
+                state = n[1]
                 if state is not None:
                     self.states[i] = torch.zeros((max_requests, *state.shape), dtype=state.dtype, device=self.device)
 
     # -- sizes --------------------------------------------------------------
     @staticmethod
     def bytes_per_page(needs, page_size: int, itemsize: int) -> int:
-        groups, _ = plan_groups(list(needs))
-        return sum(len(g.executions) * page_size * g.need.num_kv_heads * (g.need.head_dim + g.need.v_dim) * itemsize
-                   for g in groups)
+        groups, _where, _aux = plan_groups_with_aux(list(needs))
+        return sum(-(-len(g.executions) * page_size * g.need.num_kv_heads * (g.need.head_dim + g.need.v_dim) * itemsize
+                     // g.need.every) for g in groups)
 
     def num_free_pages(self, group: int = 0) -> int:
         return self.allocators[group].num_free
@@ -223,17 +261,18 @@ class CacheManager:
         return rc
 
     def pages_needed(self, rc: RequestCache, n_new: int) -> list[int]:
-        """Pages each group must add so that n_new more tokens have a place."""
+        """Pages each group must add so that n_new more tokens have a place (a group with one entry per n
+        tokens: so that the entries those tokens complete have one)."""
         total = rc.num_tokens + n_new
-        want = -(-total // self.page_size)
-        return [max(0, want - len(p)) for p in rc.pages]
+        ps = self.page_size
+        return [max(0, -(-(total // g.need.every) // ps) - len(p)) for g, p in zip(self.groups, rc.pages)]
 
     def _fits_held_pages(self, rc: RequestCache, n_new: int) -> bool:
         """The common case of a decode step: the next tokens still fit the pages the request holds."""
         room = rc.num_tokens + n_new
         ps = self.page_size
-        for p in rc.pages:
-            if room > len(p) * ps:
+        for g, p in zip(self.groups, rc.pages):
+            if room // g.need.every > len(p) * ps:
                 return False
         return True
 
@@ -265,10 +304,23 @@ class CacheManager:
                 rc.pages[g].extend(new)
                 self._mark(g, rc.slot, start, start + n, rc.pages[g])
 
+    def slot_of(self, rc: RequestCache, group: int, position: int) -> int:
+        """Flat slot (page * page_size + offset) that the token at `position` writes in `group`: its own, or in a
+        group with one entry per n tokens the slot of the entry it completes, -1 if it completes none."""
+        ps = self.page_size
+        n = self.groups[group].need.every
+        if n > 1:
+            if (position + 1) % n:
+                return -1
+            position //= n
+        return rc.pages[group][position // ps] * ps + position % ps
+
     def slot_mapping(self, rc: RequestCache, group: int, n_new: int) -> list[int]:
-        """Flat slots (page * page_size + offset) of the next n_new tokens."""
+        """Flat slots (page * page_size + offset) of the next n_new tokens (see `slot_of`)."""
         ps = self.page_size
         pages = rc.pages[group]
+        if self.groups[group].need.every > 1:
+            return [self.slot_of(rc, group, p) for p in range(rc.num_tokens, rc.num_tokens + n_new)]
         if n_new <= 16:
             return [pages[p // ps] * ps + p % ps for p in range(rc.num_tokens, rc.num_tokens + n_new)]
         pos = np.arange(rc.num_tokens, rc.num_tokens + n_new, dtype=np.int64)
@@ -383,14 +435,21 @@ class CacheManager:
     # -- views for the model --------------------------------------------------------
     def layer_caches(self, group_steps) -> list[LayerCache]:
         out = []
-        for i, (need, _state, cache_of) in enumerate(self.needs):
+        for i, n in enumerate(self.needs):
+            cache_of = n[2]
             w = self.where[i]
             st = self.states.get(i)
+            aux = None
+            if self.where_aux[i] is not None:
+                g, j = self.where_aux[i]
+                aux = LayerCache(self.k_pools[g][j], self.v_pools[g][j] if self.groups[g].need.v_dim else None,
+                                 group_steps[g], True, None)
             if w is None:
-                out.append(LayerCache(None, None, None, False, st))
+                out.append(LayerCache(None, None, None, False, st, aux))
                 continue
             g, j = w
-            out.append(LayerCache(self.k_pools[g][j], self.v_pools[g][j], group_steps[g], cache_of is None, st))
+            out.append(LayerCache(self.k_pools[g][j], self.v_pools[g][j] if self.groups[g].need.v_dim else None,
+                                  group_steps[g], cache_of is None, st, aux))
         return out
 
     # -- accounting, for tests -------------------------------------------------------

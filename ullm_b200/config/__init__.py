@@ -1,5 +1,6 @@
 from .borosun import BorosunConfig, BorosunConfigError, borosun_model_spec
 from .engine_config import EngineConfig
+from .pidenex import PidenexConfig, PidenexConfigError, pidenex_model_spec
 from .ludalix import LudalixConfig, LudalixConfigError, ludalix_model_spec
 from .qwen3 import ConfigError, Qwen3Config, qwen3_model_spec
 from .registry import (
@@ -24,10 +25,11 @@ from .specs import (
 register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict, qwen3_model_spec)
 register_architecture("Ludalix", LudalixConfig.from_dict, ludalix_model_spec)
 register_architecture("Borosun", BorosunConfig.from_dict, borosun_model_spec, reads_shapes=True)
+register_architecture("Pidenex", PidenexConfig.from_dict, pidenex_model_spec)
 
 __all__ = [
     "ARCHITECTURES", "Architecture", "BorosunConfig", "BorosunConfigError", "borosun_model_spec", "ConfigError", "EngineConfig", "FeedForwardSpec", "LayerSpec",
-    "LudalixConfig", "LudalixConfigError", "ludalix_model_spec", "MixerSpec", "ModelSpec", "NormSpec", "PositionSpec", "Qwen3Config", "ScheduleEntry", "TokenSideSpec",
+    "LudalixConfig", "LudalixConfigError", "ludalix_model_spec", "PidenexConfig", "PidenexConfigError", "pidenex_model_spec", "MixerSpec", "ModelSpec", "NormSpec", "PositionSpec", "Qwen3Config", "ScheduleEntry", "TokenSideSpec",
     "load_model_spec", "qwen3_model_spec", "read_config_json", "register_architecture",
     "resolve_architecture",
 ]

@@ -72,10 +72,15 @@ class ScheduleEntry:
     """One execution of a layer.  `layer` indexes ModelSpec.layers (a layer may
     be named by several entries: its weights are shared, each execution has a
     cache of its own).  `cache_of`, if set, is the index of an EARLIER schedule
-    entry whose cache this execution reads instead of writing one of its own."""
+    entry whose cache this execution reads instead of writing one of its own.
+    What is added to the residual stream right before this execution (a pass of a loop over layers starts here,
+    say): `add_input` the model's input as the embedding left it, `add_vector` row of the model's table of pass
+    vectors (`ModelSpec.pass_vectors`); input first, then the vector."""
 
     layer: int
     cache_of: int | None = None
+    add_input: bool = False
+    add_vector: int | None = None
 
 
 @dataclass(frozen=True)
@@ -117,6 +122,9 @@ class ModelSpec:
     logit_softcap: float | None = None
     # a per-layer token input table that blocks read through the step's context (`ctx.token_side`)
     token_side: TokenSideSpec | None = None
+    # (tensor name, rows): a table [rows, hidden] of vectors that schedule entries add to the stream
+    # (`ScheduleEntry.add_vector`); needs stream_dtype="float32"
+    pass_vectors: tuple[str, int] | None = None
 
     def validate(self) -> None:
         if not self.layers:
@@ -126,6 +134,10 @@ class ModelSpec:
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.layers)}")
+            if e.add_vector is not None and (self.pass_vectors is None or not 0 <= e.add_vector < self.pass_vectors[1]):
+                raise ValueError(f"schedule entry {i}: add_vector={e.add_vector} names no row of the pass vectors")
+            if (e.add_input or e.add_vector is not None) and self.stream_dtype != "float32":
+                raise ValueError(f"schedule entry {i}: additions to the stream need stream_dtype='float32'")
             if e.cache_of is not None:
                 if not 0 <= e.cache_of < i:
                     raise ValueError(f"schedule entry {i}: cache_of={e.cache_of} must name an earlier entry")

@@ -26,6 +26,33 @@
 #define ATT_WARPS 4
 #define ATT_O_REGS (ATT_MAX_HEAD_DIM / 32)
 
+// Further options, all off in a zeroed struct.
+//   slopes        [heads] 32-bit: the score of (query at position i, key at position j) loses slopes[h] * (i - j)
+//   v_row, v_head elements between the value rows of two slots and between two value heads inside a row, for
+//                 values that are a part of the KEY rows (v_cache = k_cache, v_row = kv heads x head_dim,
+//                 v_head = head_dim: a head's values are the first v_dim elements of its key); 0: rows of their own
+//   pool          P > 0: behind the window a query also sees ONE key / value per block of P positions that lies
+//                 wholly before the window (block b = positions bP .. bP + P - 1, seen when bP + P - 1 <= i - window);
+//                 entry b of the request sits in the pooled pages pk / pv ([*, page, kv heads, head_dim / v_dim],
+//                 pv null: the first v_dim elements of pk's rows) through a block table of their own; they are
+//                 visited first, in groups of 32 of their own, and share the softmax
+//   gate          [tokens][heads x v_dim] (row stride gate_stride): out *= sigmoid(gate) before the one rounding
+//   out_scale     multiplies the output (0 = 1); out_stride: elements between output rows (0: heads x v_dim)
+struct AttExtras {
+  const float* slopes;
+  long long v_row, v_head;
+  int pool;
+  const void* pk;
+  const void* pv;
+  const int* p_block_table;
+  int p_max_pages;
+  long long p_num_pages;
+  const void* gate;
+  long long gate_stride;
+  float out_scale;
+  long long out_stride;
+};
+
 template <typename T, int OREGS>
 __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long long q_row_stride, T* __restrict__ out,
                                                const T* __restrict__ k_cache, const T* __restrict__ v_cache,
@@ -35,7 +62,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
                                                const int* __restrict__ token_req, int tokens, int num_q, int num_kv,
                                                int head_dim, int page_size, int window, float scale,
                                                long long num_pages, int* status, int v_dim, int keep_first,
-                                               float softcap, int v_rep, float* __restrict__ out_f32) {
+                                               float softcap, int v_rep, float* __restrict__ out_f32, AttExtras ex) {
   __shared__ float qs[ATT_WARPS][ATT_MAX_HEAD_DIM];
   pdl_launch_dependents();
   pdl_wait();
@@ -51,7 +78,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
   const int h = hu / v_rep;
   const int kh = h / (num_q / num_kv);
   const int vh = v_rep > 1 ? hu - h * v_rep : kh;
-  T* o_ptr = out_f32 == nullptr ? out + ((long long)t * units_per_token + hu) * v_dim : nullptr;
+  const long long out_row = ex.out_stride > 0 ? ex.out_stride : (long long)units_per_token * v_dim;
+  T* o_ptr = out_f32 == nullptr ? out + (long long)t * out_row + (long long)hu * v_dim : nullptr;
   float* o32 = out_f32 != nullptr ? out_f32 + ((long long)t * units_per_token + hu) * v_dim : nullptr;
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   const int r = token_req[t];
@@ -77,27 +105,41 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
   for (int i = 0; i < OREGS; ++i) acc[i] = 0.f;
   const int* bt = block_table + (long long)req_slots[r] * max_pages;
   const long long kv_row = (long long)num_kv * head_dim;
-  const long long v_row = (long long)num_kv * v_dim;
-  // two stretches of keys: the kept first positions that lie below the window, then the window
+  const long long v_row = ex.v_row > 0 ? ex.v_row : (long long)num_kv * v_dim;
+  const long long v_head = ex.v_head > 0 ? ex.v_head : (long long)v_dim;
+  const float slope = ex.slopes != nullptr ? ex.slopes[h] : 0.f;
+  // three stretches of keys: the pooled blocks that lie wholly before the window, the kept first positions that
+  // lie below the window, then the window
   const int kept = min(keep_first, lo);
-  for (int part = kept > 0 ? 0 : 1; part < 2; ++part) {
-  const int first = part == 0 ? 0 : lo, last = part == 0 ? kept - 1 : pos;
+  const int pooled = ex.pool > 0 ? lo / ex.pool : 0;
+  const int* pbt = pooled > 0 ? ex.p_block_table + (long long)req_slots[r] * ex.p_max_pages : nullptr;
+  const bool pv_own = ex.pv != nullptr;
+  for (int part = pooled > 0 ? -1 : (kept > 0 ? 0 : 1); part < 2; ++part) {
+  if (part == 0 && kept <= 0) continue;
+  const int first = part == 1 ? lo : 0, last = part < 0 ? pooled - 1 : (part == 0 ? kept - 1 : pos);
+  const T* kc = part < 0 ? (const T*)ex.pk : k_cache;
+  const T* vc = part < 0 ? (pv_own ? (const T*)ex.pv : (const T*)ex.pk) : v_cache;
+  const long long vr = part < 0 ? (pv_own ? (long long)num_kv * v_dim : kv_row) : v_row;
+  const long long vhd = part < 0 ? (pv_own ? (long long)v_dim : (long long)head_dim) : v_head;
+  const int* tab = part < 0 ? pbt : bt;
+  const long long pages_here = part < 0 ? ex.p_num_pages : num_pages;
   for (int base = first; base <= last; base += 32) {
     const int key = base + lane;
     const bool valid = key <= last;
     long long slot = -1;
     float s = -INFINITY;
     if (valid) {
-      const int page = bt[key / page_size];
-      if (page < 0 || page >= num_pages) {
+      const int page = tab[key / page_size];
+      if (page < 0 || page >= pages_here) {
         ullm_report(status, ULLM_STATUS_PAGE, t, page);
       } else {
         slot = (long long)page * page_size + key % page_size;
-        const T* kp = k_cache + slot * kv_row + (long long)kh * head_dim;
+        const T* kp = kc + slot * kv_row + (long long)kh * head_dim;
         float d = 0.f;
         for (int e = 0; e < head_dim; ++e) d += qv[e] * to_f32(kp[e]);
         s = d * scale;
         if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
+        if (part >= 0) s -= slope * (float)(pos - key);
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -111,7 +153,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
       const float pj = __shfl_sync(0xffffffffu, p, j);
       const long long sj = __shfl_sync(0xffffffffu, slot, j);
       if (sj < 0) continue;
-      const T* vp = v_cache + sj * v_row + (long long)vh * v_dim;
+      const T* vp = vc + sj * vr + (long long)vh * vhd;
 #pragma unroll
       for (int i = 0; i < OREGS; ++i) {
         const int e = lane + 32 * i;
@@ -121,13 +163,16 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
     m = m_new;
   }
   }
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+  const float inv = (l > 0.f ? 1.f / l : 0.f) * (ex.out_scale != 0.f ? ex.out_scale : 1.f);
+  const T* gate = ex.gate != nullptr ? (const T*)ex.gate + (long long)t * ex.gate_stride + (long long)hu * v_dim : nullptr;
 #pragma unroll
   for (int i = 0; i < OREGS; ++i) {
     const int e = lane + 32 * i;
     if (e < v_dim) {
-      if (o32 != nullptr) o32[e] = acc[i] * inv;
-      else o_ptr[e] = from_f32<T>(acc[i] * inv);
+      float o = acc[i] * inv;
+      if (gate != nullptr) o /= 1.f + expf(-to_f32(gate[e]));
+      if (o32 != nullptr) o32[e] = o;
+      else o_ptr[e] = from_f32<T>(o);
     }
   }
 }
@@ -206,7 +251,8 @@ static int launch_generic(const void* q, long long q_row_stride, void* out, cons
                           const int* block_table, int max_pages, const int* req_slots, const int* cu_q,
                           const int* kv_len, const int* token_req, int tokens, int num_q, int num_kv, int head_dim, int page_size,
                           int window, float scale, long long num_pages, int* status, cudaStream_t st, int v_dim,
-                          int keep_first, float softcap = 0.f, int v_rep = 1, float* out_f32 = nullptr) {
+                          int keep_first, float softcap = 0.f, int v_rep = 1, float* out_f32 = nullptr,
+                          AttExtras ex = AttExtras{}) {
   const long long units = (long long)tokens * num_q * v_rep;
   const long long blocks = (units + ATT_WARPS - 1) / ATT_WARPS;
   if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
@@ -214,7 +260,7 @@ static int launch_generic(const void* q, long long q_row_stride, void* out, cons
   rc = ullm_launch_kernel(paged_attention_generic_kernel<T, OREGS>, dim3((int)blocks), dim3(ATT_WARPS * 32), 0, st, \
       (const T*)q, q_row_stride, (T*)out, (const T*)k_cache, (const T*)v_cache, block_table, max_pages, req_slots,  \
       cu_q, kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages, status,       \
-      v_dim, keep_first, softcap, v_rep, out_f32)
+      v_dim, keep_first, softcap, v_rep, out_f32, ex)
   int rc = ULLM_OK;
   if (v_dim <= 32) LAUNCH(1);
   else if (v_dim <= 64) LAUNCH(2);
@@ -256,6 +302,63 @@ extern "C" int ullm_paged_attention_generic_ex2(int dtype, const void* q, long l
     return launch_generic<__half>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
                                   kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages,
                                   status, st, v_dim, keep_first, softcap, v_rep, out_parts);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+// The general kernel with the further options of `AttExtras` (see there): distance slopes, values inside the key
+// rows (`values_in_keys`), pooled blocks behind the window, an output gate, a scale and a row stride of the output.
+extern "C" int ullm_paged_attention_generic_ex3(int dtype, const void* q, long long q_row_stride, void* out,
+                                                const void* k_cache, const void* v_cache, const int* block_table,
+                                                int max_pages, const int* req_slots, const int* cu_q,
+                                                const int* kv_len, const int* token_req, int tokens, int num_q,
+                                                int num_kv, int head_dim, int page_size, int window, float scale,
+                                                long long num_pages, int* status, void* stream, int v_dim,
+                                                int keep_first, float softcap, const float* slopes,
+                                                int values_in_keys, int pool, const void* pk, const void* pv,
+                                                const int* p_block_table, int p_max_pages, long long p_num_pages,
+                                                const void* gate, long long gate_stride, float out_scale,
+                                                long long out_stride) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || num_q <= 0 || num_kv <= 0 || head_dim <= 0 || page_size <= 0 || max_pages <= 0)
+    return ULLM_ERR_BAD_SIZE;
+  if (num_q % num_kv != 0 || head_dim > ATT_MAX_HEAD_DIM || window < 0 || v_dim <= 0 || v_dim > ATT_MAX_HEAD_DIM ||
+      keep_first < 0 || softcap < 0.f || pool < 0)
+    return ULLM_ERR_UNSUPPORTED;
+  if (values_in_keys && v_dim > head_dim) return ULLM_ERR_BAD_SIZE;
+  if (pool > 0 && (window <= 0 || pk == nullptr || p_block_table == nullptr || p_max_pages <= 0 || keep_first > 0 ||
+                   slopes != nullptr))
+    return ULLM_ERR_UNSUPPORTED;
+  if (out_stride != 0 && out_stride < (long long)num_q * v_dim) return ULLM_ERR_BAD_SIZE;
+  if (tokens == 0) return ULLM_OK;
+  AttExtras ex = {};
+  ex.slopes = slopes;
+  if (values_in_keys) {
+    v_cache = k_cache;
+    ex.v_row = (long long)num_kv * head_dim;
+    ex.v_head = head_dim;
+  }
+  ex.pool = pool;
+  ex.pk = pk;
+  ex.pv = pv;
+  ex.p_block_table = p_block_table;
+  ex.p_max_pages = p_max_pages;
+  ex.p_num_pages = p_num_pages;
+  ex.gate = gate;
+  ex.gate_stride = gate_stride;
+  ex.out_scale = out_scale;
+  ex.out_stride = out_stride;
+  if (dtype == ULLM_DTYPE_F32)
+    return launch_generic<float>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                 kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages,
+                                 status, st, v_dim, keep_first, softcap, 1, nullptr, ex);
+  if (dtype == ULLM_DTYPE_BF16)
+    return launch_generic<__nv_bfloat16>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                         kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale,
+                                         num_pages, status, st, v_dim, keep_first, softcap, 1, nullptr, ex);
+  if (dtype == ULLM_DTYPE_F16)
+    return launch_generic<__half>(q, q_row_stride, out, k_cache, v_cache, block_table, max_pages, req_slots, cu_q,
+                                  kv_len, token_req, tokens, num_q, num_kv, head_dim, page_size, window, scale, num_pages,
+                                  status, st, v_dim, keep_first, softcap, 1, nullptr, ex);
   return ULLM_ERR_BAD_DTYPE;
 }
 

@@ -1,0 +1,234 @@
+// Preparation kernels of three attention forms, each in front of the general attention kernel:
+//
+//   kv_shared_prepare   attention whose VALUES ARE ITS KEYS as projected (no value projection), with an optional
+//                       RMS norm of q and of k over the WHOLE projection (all heads at once, one weight per
+//                       channel): q is normed in place, the normed k goes to the key pages and the k as projected
+//                       to the value pages; without the norm only the key pages are written (the values are read
+//                       from them)
+//   pool_blocks         mean key / value of each block of P positions whose last position arrived in this step,
+//                       read from the pages as they hold them, written to pooled pages of their own
+//   latent_prepare      latent attention in its absorbed form: the latent c = RMSnorm(first `rank` columns of the
+//                       down projection) and the rotated shared key part form ONE key row [c | k_rot] of a single
+//                       kv head (the values are its first `rank` elements); a query row per head is
+//                       [q_h W_uk,h (from a batched product) | rotated q_rot,h]
+//
+// Rotation: neighbours (2i, 2i + 1), i < dims / 2, turn by the 32-bit angle position * f_i (f_i from a table built
+// in 64-bit); sincosf is the accurate form.  Sums and norms are 32-bit; one rounding at each store.
+#include "common.cuh"
+
+// One block per token.  qk: [tokens][stride], q in columns 0 .. q_size-1, k in q_size .. q_size + kv_size - 1.
+template <typename T>
+__global__ void kv_shared_prepare_kernel(T* __restrict__ qk, long long stride, int q_size, int kv_size,
+                                         const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                                         const int* __restrict__ slot_mapping, T* __restrict__ k_pages,
+                                         T* __restrict__ v_pages, long long num_slots, int* status) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  T* q = qk + (long long)t * stride;
+  T* k = q + q_size;
+  long long slot = slot_mapping != nullptr ? slot_mapping[t] : -1;
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) ullm_report(status, ULLM_STATUS_SLOT, t, (int)slot);
+    slot = -1;
+  }
+  if (wq != nullptr) {
+    float acc = 0.f;
+    for (int c = threadIdx.x; c < q_size; c += blockDim.x) {
+      const float v = to_f32(q[c]);
+      acc += v * v;
+    }
+    const float rq = 1.f / sqrtf(block_sum(acc, scratch) / (float)q_size + eps);
+    for (int c = threadIdx.x; c < q_size; c += blockDim.x) q[c] = from_f32<T>(to_f32(q[c]) * rq * wq[c]);
+    acc = 0.f;
+    for (int c = threadIdx.x; c < kv_size; c += blockDim.x) {
+      const float v = to_f32(k[c]);
+      acc += v * v;
+    }
+    const float rk = 1.f / sqrtf(block_sum(acc, scratch) / (float)kv_size + eps);
+    if (slot >= 0) {
+      for (int c = threadIdx.x; c < kv_size; c += blockDim.x) {
+        const T raw = k[c];
+        k_pages[slot * kv_size + c] = from_f32<T>(to_f32(raw) * rk * wk[c]);
+        if (v_pages != nullptr) v_pages[slot * kv_size + c] = raw;
+      }
+    }
+  } else if (slot >= 0) {
+    for (int c = threadIdx.x; c < kv_size; c += blockDim.x) {
+      const T raw = k[c];
+      k_pages[slot * kv_size + c] = raw;
+      if (v_pages != nullptr) v_pages[slot * kv_size + c] = raw;
+    }
+  }
+}
+
+// One block per token; a token whose pooled slot is -1 completes no block.  The block's positions are
+// pos - pool + 1 .. pos of the token's request, found through the request's row of the block table.
+template <typename T>
+__global__ void pool_blocks_kernel(const int* __restrict__ positions, const int* __restrict__ token_req,
+                                   const int* __restrict__ req_slots, const int* __restrict__ block_table,
+                                   int max_pages, int page_size, long long num_pages, const T* __restrict__ k_pages,
+                                   const T* __restrict__ v_pages, int row, int v_row,
+                                   const int* __restrict__ pool_slots, long long num_pool_slots,
+                                   T* __restrict__ pk_pages, T* __restrict__ pv_pages, int pool, int* status) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const long long dst = pool_slots[t];
+  const int r = token_req[t];
+  if (dst < 0 || r < 0) return;
+  if (dst >= num_pool_slots) {
+    if (threadIdx.x == 0) ullm_report(status, ULLM_STATUS_SLOT, t, (int)dst);
+    return;
+  }
+  const int pos = positions[t];
+  const int* bt = block_table + (long long)req_slots[r] * max_pages;
+  const float inv = 1.f / (float)pool;
+  const int cols = row + (v_pages != nullptr ? v_row : 0);
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const bool is_v = c >= row;
+    float acc = 0.f;
+    bool ok = true;
+    for (int j = pos - pool + 1; j <= pos; ++j) {
+      const int page = j >= 0 ? bt[j / page_size] : -1;
+      if (page < 0 || page >= num_pages) {
+        ok = false;
+        ullm_report(status, ULLM_STATUS_PAGE, t, page);
+        break;
+      }
+      const long long slot = (long long)page * page_size + j % page_size;
+      acc += is_v ? to_f32(v_pages[slot * v_row + (c - row)]) : to_f32(k_pages[slot * row + c]);
+    }
+    if (!ok) continue;
+    if (is_v) pv_pages[dst * v_row + (c - row)] = from_f32<T>(acc * inv);
+    else pk_pages[dst * row + c] = from_f32<T>(acc * inv);
+  }
+}
+
+// One block per token.  q_full [tokens][heads][dim + rot] (the query up-projection), q_lat [heads][tokens][rank]
+// (q_h W_uk,h), dkv [tokens][rank + rot]; q_out [tokens][heads][rank + rot]; key pages [*][rank + rot].
+template <typename T>
+__global__ void latent_prepare_kernel(const T* __restrict__ q_full, const T* __restrict__ q_lat,
+                                      const T* __restrict__ dkv, T* __restrict__ q_out, int tokens, int heads,
+                                      int dim, int rot, int rank, int rot_dims, const float* __restrict__ w_c,
+                                      float eps, const float* __restrict__ inv_freq,
+                                      const int* __restrict__ positions, const int* __restrict__ slot_mapping,
+                                      T* __restrict__ k_pages, long long num_slots, int* status) {
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float p = (float)positions[t];
+  const int kw = rank + rot;
+  // queries: the absorbed part is copied, the rotated part turned
+  for (int i = threadIdx.x; i < heads * rank; i += blockDim.x) {
+    const int h = i / rank, c = i - h * rank;
+    q_out[((long long)t * heads + h) * kw + c] = q_lat[((long long)h * tokens + t) * rank + c];
+  }
+  for (int i = threadIdx.x; i < heads * rot; i += blockDim.x) {
+    const int h = i / rot, c = i - h * rot;
+    const T* src = q_full + ((long long)t * heads + h) * (dim + rot) + dim;
+    float v = to_f32(src[c]);
+    if (c < rot_dims) {
+      float sn, cs;
+      sincosf(p * inv_freq[c >> 1], &sn, &cs);
+      const float other = to_f32(src[c ^ 1]);
+      v = (c & 1) ? v * cs + other * sn : v * cs - other * sn;
+    }
+    q_out[((long long)t * heads + h) * kw + rank + c] = from_f32<T>(v);
+  }
+  // the key row: normed latent, rotated shared part
+  long long slot = slot_mapping != nullptr ? slot_mapping[t] : -1;
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) ullm_report(status, ULLM_STATUS_SLOT, t, (int)slot);
+    slot = -1;
+  }
+  const T* row = dkv + (long long)t * kw;
+  float acc = 0.f;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    const float v = to_f32(row[c]);
+    acc += v * v;
+  }
+  const float rstd = 1.f / sqrtf(block_sum(acc, scratch) / (float)rank + eps);
+  if (slot < 0) return;
+  T* dst = k_pages + slot * kw;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) dst[c] = from_f32<T>(to_f32(row[c]) * rstd * w_c[c]);
+  for (int c = threadIdx.x; c < rot; c += blockDim.x) {
+    float v = to_f32(row[rank + c]);
+    if (c < rot_dims) {
+      float sn, cs;
+      sincosf(p * inv_freq[c >> 1], &sn, &cs);
+      const float other = to_f32(row[rank + (c ^ 1)]);
+      v = (c & 1) ? v * cs + other * sn : v * cs - other * sn;
+    }
+    dst[rank + c] = from_f32<T>(v);
+  }
+}
+
+static inline int prep_threads(int cols) {
+  int threads = 32;
+  while (threads < 256 && threads * 2 < cols) threads <<= 1;
+  return threads;
+}
+
+// `wq` / `wk` null: no norm.  `v_pages` null: only the key pages are written.  `slot_mapping` null: nothing is stored.
+extern "C" int ullm_kv_shared_prepare(int dtype, void* qk, long long stride, int tokens, int q_size, int kv_size,
+                                      const float* wq, const float* wk, float eps, const int* slot_mapping,
+                                      void* k_pages, void* v_pages, long long num_slots, int* status, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || q_size <= 0 || kv_size <= 0 || stride < q_size + kv_size) return ULLM_ERR_BAD_SIZE;
+  if ((wq == nullptr) != (wk == nullptr)) return ULLM_ERR_BAD_SIZE;
+  if (tokens == 0) return ULLM_OK;
+  const dim3 grid(tokens), block(prep_threads(q_size));
+#define KSP_GO(T)                                                                                                  \
+  return ullm_launch_kernel(kv_shared_prepare_kernel<T>, grid, block, 0, st, (T*)qk, stride, q_size, kv_size, wq, wk, \
+                            eps, slot_mapping, (T*)k_pages, (T*)v_pages, num_slots, status)
+  if (dtype == ULLM_DTYPE_F32) KSP_GO(float);
+  if (dtype == ULLM_DTYPE_BF16) KSP_GO(__nv_bfloat16);
+  if (dtype == ULLM_DTYPE_F16) KSP_GO(__half);
+#undef KSP_GO
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+// `v_pages` / `pv_pages` null: the values are the keys (one pooled row serves both).
+extern "C" int ullm_pool_blocks(int dtype, const int* positions, const int* token_req, const int* req_slots,
+                                const int* block_table, int max_pages, int page_size, long long num_pages,
+                                const void* k_pages, const void* v_pages, int row, int v_row, const int* pool_slots,
+                                long long num_pool_slots, void* pk_pages, void* pv_pages, int pool, int tokens,
+                                int* status, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || row <= 0 || pool <= 0 || page_size <= 0 || max_pages <= 0) return ULLM_ERR_BAD_SIZE;
+  if ((v_pages == nullptr) != (pv_pages == nullptr) || (v_pages != nullptr && v_row <= 0)) return ULLM_ERR_BAD_SIZE;
+  if (tokens == 0) return ULLM_OK;
+  const dim3 grid(tokens), block(prep_threads(row));
+#define PB_GO(T)                                                                                                    \
+  return ullm_launch_kernel(pool_blocks_kernel<T>, grid, block, 0, st, positions, token_req, req_slots, block_table, \
+                            max_pages, page_size, num_pages, (const T*)k_pages, (const T*)v_pages, row, v_row,       \
+                            pool_slots, num_pool_slots, (T*)pk_pages, (T*)pv_pages, pool, status)
+  if (dtype == ULLM_DTYPE_F32) PB_GO(float);
+  if (dtype == ULLM_DTYPE_BF16) PB_GO(__nv_bfloat16);
+  if (dtype == ULLM_DTYPE_F16) PB_GO(__half);
+#undef PB_GO
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+extern "C" int ullm_latent_prepare(int dtype, const void* q_full, const void* q_lat, const void* dkv, void* q_out,
+                                   int tokens, int heads, int dim, int rot, int rank, int rot_dims, const float* w_c,
+                                   float eps, const float* inv_freq, const int* positions, const int* slot_mapping,
+                                   void* k_pages, long long num_slots, int* status, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || heads <= 0 || dim <= 0 || rot < 0 || rank <= 0) return ULLM_ERR_BAD_SIZE;
+  if (rot_dims < 0 || rot_dims > rot || rot_dims % 2 || (rot_dims > 0 && inv_freq == nullptr)) return ULLM_ERR_BAD_SIZE;
+  if (tokens == 0) return ULLM_OK;
+  const dim3 grid(tokens), block(prep_threads(heads * rank / 4));
+#define LP_GO(T)                                                                                                  \
+  return ullm_launch_kernel(latent_prepare_kernel<T>, grid, block, 0, st, (const T*)q_full, (const T*)q_lat,       \
+                            (const T*)dkv, (T*)q_out, tokens, heads, dim, rot, rank, rot_dims, w_c, eps, inv_freq, \
+                            positions, slot_mapping, (T*)k_pages, num_slots, status)
+  if (dtype == ULLM_DTYPE_F32) LP_GO(float);
+  if (dtype == ULLM_DTYPE_BF16) LP_GO(__nv_bfloat16);
+  if (dtype == ULLM_DTYPE_F16) LP_GO(__half);
+#undef LP_GO
+  return ULLM_ERR_BAD_DTYPE;
+}

@@ -256,6 +256,15 @@ class Kernels:
             "ullm_paged_attention_generic_ex2": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P, I, I,
                                                  F, P],
             "ullm_mix_heads": [I, P, P, P, I, I, I, I, P],
+            "ullm_paged_attention_generic_ex3": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P, I, I,
+                                                 F, P, I, I, P, P, P, I, LL, P, LL, F, LL],
+            "ullm_norm_add_norm": [I, P, P, P, I, I, F, F, I, P, P, P, F, I, I, P, P],
+            "ullm_norm_rows": [I, P, P, P, P, I, I, I, F, I, P, P],
+            "ullm_xielu": [I, P, P, LL, P, P],
+            "ullm_kv_shared_prepare": [I, P, LL, I, I, I, P, P, F, P, P, P, LL, P, P],
+            "ullm_pool_blocks": [I, P, P, P, P, I, I, LL, P, P, I, I, P, LL, P, P, I, I, P, P],
+            "ullm_latent_prepare": [I, P, P, P, P, I, I, I, I, I, I, P, F, P, P, P, P, LL, P, P],
+            "ullm_mingru": [I, P, LL, I, I, I, P, P, P, LL, P, P, P, P, LL, F, I, I, I, P, P],
             "ullm_gla_recurrence": [I, P, LL, I, I, I, P, LL, P, F, F, P, LL, P, P, P, P, I, I, I, I, I, I, P, P],
             "ullm_head_norm_gate": [I, P, P, LL, P, P, I, I, I, F, I, I, P],
             "ullm_moe_route": [P, P, P, I, I, I, I, I, P],
@@ -269,6 +278,8 @@ class Kernels:
             fn = getattr(L, name)
             fn.argtypes = args
             fn.restype = c_int
+        L.ullm_mingru_chunk.argtypes = []
+        L.ullm_mingru_chunk.restype = c_int
         L.ullm_moe_force_plain.argtypes = [I]
         L.ullm_moe_force_plain.restype = None
         L.ullm_mlstm_supported.argtypes = [I, I, I]
@@ -824,6 +835,238 @@ class Kernels:
             raise KernelError(f"act_mul_clamped: gate_up {tuple(gate_up.shape)}, out {tuple(out.shape)}")
         self._check(self.lib.ullm_act_mul_clamped(_DT[gate_up.dtype], _ptr(gate_up), _ptr(out), rows, inter, float(limit),
                                                   float(alpha), _stream()), "act_mul_clamped")
+
+    # -- norms on both sides of a sub-layer, on a 32-bit stream -------------------
+    @_timed("add_rmsnorm")
+    def norm_add_norm(self, stream, a=None, weight=None, eps: float = 0.0, mult: float = 1.0, center: bool = False,
+                      extra_rows=None, extra_vec=None, next_norm=None):
+        """stream (float32, in place) += mult * weight * n(a), then += extra_rows, then += extra_vec (each part
+        optional); `next_norm` = (weight2, eps2, center2, out): out = weight2 * n2(stream) rounded to out's dtype.
+        n(v) = v / sqrt(mean(v^2) + eps), with `center` (v - mean) / sqrt(mean((v - mean)^2) + eps)."""
+        _need(stream, "stream", torch.float32)
+        rows, cols = stream.shape
+        if a is not None:
+            _need(a, "a")
+            _need(weight, "weight", torch.float32)
+            if a.shape != stream.shape or weight.numel() != cols:
+                raise KernelError(f"norm_add_norm: a {tuple(a.shape)}, stream {tuple(stream.shape)}, weight {tuple(weight.shape)}")
+        if extra_rows is not None:
+            _need(extra_rows, "extra_rows", torch.float32)
+            if extra_rows.shape != stream.shape:
+                raise KernelError("norm_add_norm: the added rows' shape differs from the stream's")
+        if extra_vec is not None:
+            _need(extra_vec, "extra_vec", torch.float32)
+            if extra_vec.numel() != cols:
+                raise KernelError("norm_add_norm: the added vector's length differs from the stream's width")
+        w2 = out = None
+        eps2, center2 = 0.0, False
+        if next_norm is not None:
+            w2, eps2, center2, out = next_norm
+            _need(w2, "next norm weight", torch.float32)
+            _need(out, "out")
+            if out.shape != stream.shape or w2.numel() != cols:
+                raise KernelError("norm_add_norm: the next norm's shapes differ")
+        self._check(self.lib.ullm_norm_add_norm(
+            _DT[a.dtype] if a is not None else 0, _ptr(a), _ptr(stream), _ptr(weight), rows, cols, float(eps), float(mult),
+            int(bool(center)), _ptr(extra_rows), _ptr(extra_vec), _ptr(w2), float(eps2), int(bool(center2)),
+            _DT[out.dtype] if out is not None else 0, _ptr(out), _stream()), f"norm_add_norm (row length {cols})")
+
+    @_timed("add_rmsnorm")
+    def norm_rows(self, stream, rows, weight, eps: float, out, center: bool = False):
+        """out[r] = weight * n(stream[rows[r]]) (float32 stream; `rows` int32, or None for all rows in order),
+        rounded to out's dtype; n as in `norm_add_norm`."""
+        _need(stream, "stream", torch.float32)
+        _need(weight, "weight", torch.float32)
+        _need(out, "out")
+        R, C = out.shape
+        if stream.shape[1] != C or weight.numel() != C or (rows is None and stream.shape[0] < R):
+            raise KernelError(f"norm_rows: stream {tuple(stream.shape)}, out {tuple(out.shape)}")
+        if rows is not None:
+            _need(rows, "rows", torch.int32)
+            if rows.numel() < R:
+                raise KernelError("norm_rows: fewer row indices than output rows")
+        self._check(self.lib.ullm_norm_rows(_DT[out.dtype], _ptr(stream), _ptr(rows), _ptr(weight), _ptr(out), R, C,
+                                            stream.shape[0], float(eps), int(bool(center)), _ptr(self.status),
+                                            _stream()), f"norm_rows (row length {C})")
+
+    @_timed("act_mul")
+    def xielu(self, x, pq, out):
+        """out = softplus(p) z^2 + z / 2 for z > 0, (1/2 + softplus(q)) (e^z - 1 - z) + z / 2 otherwise, with
+        (p, q) = `pq` (float32 [2] on the device)."""
+        _need(x, "x")
+        _need(out, "out", x.dtype)
+        _need(pq, "pq", torch.float32)
+        if out.shape != x.shape or pq.numel() != 2:
+            raise KernelError(f"xielu: x {tuple(x.shape)}, out {tuple(out.shape)}, pq {tuple(pq.shape)}")
+        self._check(self.lib.ullm_xielu(_DT[x.dtype], _ptr(x), _ptr(out), x.numel(), _ptr(pq), _stream()), "xielu")
+
+    # -- attention whose values are its keys; pooled blocks; latent attention ------
+    @_timed("qk_norm_rope_store")
+    def kv_shared_prepare(self, qk, q_size: int, kv_size: int, q_w, k_w, eps: float, slot_mapping, k_pages, v_pages):
+        """qk [T, >= q_size + kv_size] holds q | k as projected.  With weights: q <- RMSnorm over all its q_size
+        columns (in place), the likewise normed k goes to the key pages and k as projected to the value pages.
+        Without: k goes to the key pages (and to `v_pages` if given)."""
+        _need(qk, "qk", contiguous=False)
+        _need(k_pages, "k_pages", qk.dtype)
+        if qk.stride(1) != 1 or qk.shape[1] < q_size + kv_size:
+            raise KernelError(f"kv_shared_prepare: qk {tuple(qk.shape)} for {q_size} + {kv_size} columns")
+        if (q_w is None) != (k_w is None):
+            raise KernelError("kv_shared_prepare: the norm weights of q and k come together")
+        if q_w is not None:
+            _need(q_w, "q_w", torch.float32)
+            _need(k_w, "k_w", torch.float32)
+            if q_w.numel() != q_size or k_w.numel() != kv_size:
+                raise KernelError("kv_shared_prepare: the norm weights do not fit the projections")
+        if v_pages is not None:
+            _need(v_pages, "v_pages", qk.dtype)
+            if v_pages.numel() != k_pages.numel():
+                raise KernelError("kv_shared_prepare: value pages of another size than the key pages")
+        if slot_mapping is not None:
+            _need(slot_mapping, "slot_mapping", torch.int32)
+        self._check(self.lib.ullm_kv_shared_prepare(
+            _DT[qk.dtype], _ptr(qk), qk.stride(0), qk.shape[0], q_size, kv_size, _ptr(q_w), _ptr(k_w), float(eps),
+            _ptr(slot_mapping), _ptr(k_pages), _ptr(v_pages), k_pages.numel() // kv_size, _ptr(self.status), _stream()),
+            "kv_shared_prepare")
+
+    @_timed("qk_norm_rope_store")
+    def pool_blocks(self, positions, token_req, req_slots, block_table, page_size: int, k_pages, v_pages, pool_slots,
+                    pk_pages, pv_pages, pool: int):
+        """For every token whose `pool_slots` entry is not -1 (it completes a block of `pool` positions): the mean
+        of the block's key rows (and value rows, when the values have pages of their own) as the pages hold them,
+        written to that slot of the pooled pages."""
+        for t, n in ((positions, "positions"), (token_req, "token_req"), (req_slots, "req_slots"),
+                     (block_table, "block_table"), (pool_slots, "pool_slots")):
+            _need(t, n, torch.int32)
+        _need(k_pages, "k_pages")
+        _need(pk_pages, "pk_pages", k_pages.dtype)
+        row = k_pages.shape[-2] * k_pages.shape[-1]
+        v_row = 0
+        if (v_pages is None) != (pv_pages is None):
+            raise KernelError("pool_blocks: value pages and pooled value pages come together")
+        if v_pages is not None:
+            _need(v_pages, "v_pages", k_pages.dtype)
+            _need(pv_pages, "pv_pages", k_pages.dtype)
+            v_row = v_pages.shape[-2] * v_pages.shape[-1]
+        T = pool_slots.numel()
+        self._check(self.lib.ullm_pool_blocks(
+            _DT[k_pages.dtype], _ptr(positions), _ptr(token_req), _ptr(req_slots), _ptr(block_table), block_table.shape[1],
+            page_size, k_pages.numel() // (page_size * row), _ptr(k_pages), _ptr(v_pages), row, v_row, _ptr(pool_slots),
+            pk_pages.numel() // row, _ptr(pk_pages), _ptr(pv_pages), int(pool), T, _ptr(self.status), _stream()),
+            "pool_blocks")
+
+    @_timed("qk_norm_rope_store")
+    def latent_prepare(self, q_full, q_lat, dkv, q_out, heads: int, dim: int, rot: int, rank: int, rot_dims: int, c_w,
+                       eps: float, inv_freq, positions, slot_mapping, k_pages):
+        """Latent attention, absorbed form.  q_full [T, heads x (dim + rot)], q_lat [heads, T, rank] (each head's
+        unrotated query times its key up-projection), dkv [T, rank + rot].  Leaves q_out [T, heads x (rank + rot)]
+        = [q_lat | rotated q_rot] per head and the key row [RMSnorm(dkv[:rank]) x c_w | rotated dkv[rank:]] in
+        `k_pages` at the tokens' slots.  Neighbouring dimensions (2i, 2i + 1) below `rot_dims` are rotated."""
+        T = dkv.shape[0]
+        for t, n in ((q_full, "q_full"), (q_lat, "q_lat"), (dkv, "dkv"), (q_out, "q_out"), (k_pages, "k_pages")):
+            _need(t, n, dkv.dtype)
+        _need(c_w, "c_w", torch.float32)
+        _need(positions, "positions", torch.int32)
+        if (q_full.shape != (T, heads * (dim + rot)) or q_lat.shape != (heads, T, rank) or dkv.shape[1] != rank + rot
+                or q_out.shape != (T, heads * (rank + rot)) or c_w.numel() != rank or k_pages.shape[-1] != rank + rot):
+            raise KernelError("latent_prepare: shapes do not fit the sizes")
+        if rot_dims:
+            _need(inv_freq, "inv_freq", torch.float32)
+            if inv_freq.numel() < rot_dims // 2:
+                raise KernelError("latent_prepare: the frequency table is too short")
+        if slot_mapping is not None:
+            _need(slot_mapping, "slot_mapping", torch.int32)
+        self._check(self.lib.ullm_latent_prepare(
+            _DT[dkv.dtype], _ptr(q_full), _ptr(q_lat), _ptr(dkv), _ptr(q_out), T, heads, dim, rot, rank, rot_dims,
+            _ptr(c_w), float(eps), _ptr(inv_freq), _ptr(positions), _ptr(slot_mapping), _ptr(k_pages),
+            k_pages.numel() // (rank + rot), _ptr(self.status), _stream()), "latent_prepare")
+
+    @_timed("attention")
+    def windowed_attention(self, q, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req, num_q: int,
+                           num_kv: int, head_dim: int, v_dim: int, page_size: int, window: int, scale: float, *,
+                           slopes=None, pool: int = 0, pooled=None, gate=None, out_scale: float = 1.0):
+        """The general attention kernel with its further options.  `v_pages` None: a head's values are the first
+        `v_dim` elements of its key rows.  `slopes` (float32 [num_q]): score(i, j) -= slopes[h] (i - j).  `pool` P
+        with `pooled` = (pooled key pages, pooled value pages or None, their block table): blocks of P positions
+        that lie wholly before the window are seen through one mean key / value each.  `gate` [T, num_q x v_dim]
+        (row stride free): out *= sigmoid(gate).  `out` [T, num_q x v_dim] may be a column range of wider rows."""
+        _need(q, "q", contiguous=False)
+        _need(out, "out", q.dtype, contiguous=False)
+        _need(k_pages, "k_pages", q.dtype)
+        for t, n in ((block_table, "block_table"), (req_slots, "req_slots"), (cu_q, "cu_q"), (kv_len, "kv_len"),
+                     (token_req, "token_req")):
+            _need(t, n, torch.int32)
+        T = out.shape[0]
+        if q.stride(1) != 1 or out.stride(1) != 1 or out.shape[1] != num_q * v_dim or q.shape[1] < num_q * head_dim:
+            raise KernelError(f"windowed_attention: q {tuple(q.shape)}, out {tuple(out.shape)}")
+        if k_pages.shape[-3:] != (page_size, num_kv, head_dim):
+            raise KernelError(f"windowed_attention: key pages {tuple(k_pages.shape)}")
+        if v_pages is not None:
+            _need(v_pages, "v_pages", q.dtype)
+            if v_pages.shape[-3:] != (page_size, num_kv, v_dim):
+                raise KernelError(f"windowed_attention: value pages {tuple(v_pages.shape)}")
+        elif v_dim > head_dim:
+            raise KernelError("windowed_attention: values inside the key rows cannot be wider than the keys")
+        if slopes is not None:
+            _need(slopes, "slopes", torch.float32)
+            if slopes.numel() != num_q:
+                raise KernelError("windowed_attention: one slope per head")
+        pk = pv = pbt = None
+        if pool:
+            pk, pv, pbt = pooled
+            _need(pk, "pooled key pages", q.dtype)
+            _need(pbt, "pooled block table", torch.int32)
+            if pk.shape[-3:] != (page_size, num_kv, head_dim) or (pv is None) != (v_pages is None):
+                raise KernelError("windowed_attention: the pooled pages do not fit the pages")
+            if pv is not None:
+                _need(pv, "pooled value pages", q.dtype)
+        if gate is not None:
+            _need(gate, "gate", q.dtype, contiguous=False)
+            if gate.stride(1) != 1 or gate.shape != (T, num_q * v_dim):
+                raise KernelError(f"windowed_attention: gate {tuple(gate.shape)}")
+        self.attention_path = "generic"
+        self._check(self.lib.ullm_paged_attention_generic_ex3(
+            _DT[q.dtype], _ptr(q), q.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+            block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), _ptr(token_req), T, num_q, num_kv, head_dim,
+            page_size, int(window), float(scale), k_pages.numel() // (page_size * num_kv * head_dim), _ptr(self.status),
+            _stream(), v_dim, 0, 0.0, _ptr(slopes), int(v_pages is None), int(pool), _ptr(pk), _ptr(pv), _ptr(pbt),
+            pbt.shape[1] if pbt is not None else 0,
+            pk.numel() // (page_size * num_kv * head_dim) if pk is not None else 0, _ptr(gate),
+            gate.stride(0) if gate is not None else 0, float(out_scale), out.stride(0)),
+            f"windowed_attention (head_dim {head_dim}, values {v_dim}, pool {pool})")
+
+    # -- minGRU -------------------------------------------------------------------
+    @_timed("mingru")
+    def mingru(self, azg, a_off: int, x_off: int, g_off: int, b_z, b_x, state, cu_q, req_slots, token_req, out,
+               out_scale: float, requests: int, max_q: int, fold=None):
+        """azg (float32 [T, >= 3 width]): the gate's, the candidate's and the output gate's projections side by side;
+        state (float32 [slots, width]) is carried; out [T, width] (any row stride) = out_scale * S_t * silu(g_t).
+        `fold`: scratch for the chunked form (float32, `mingru_fold_floats`), taken for portions longer than a chunk."""
+        _need(azg, "azg", torch.float32)
+        _need(state, "state", torch.float32)
+        _need(b_z, "b_z", torch.float32)
+        _need(b_x, "b_x", torch.float32)
+        _need(out, "out", contiguous=False)
+        for t, n in ((cu_q, "cu_q"), (req_slots, "req_slots"), (token_req, "token_req")):
+            _need(t, n, torch.int32)
+        width = state.shape[1]
+        if out.shape[1] != width or out.stride(1) != 1 or max(a_off, x_off, g_off) + width > azg.shape[1]:
+            raise KernelError(f"mingru: azg {tuple(azg.shape)}, out {tuple(out.shape)}, width {width}")
+        if fold is not None:
+            _need(fold, "fold", torch.float32)
+            if fold.numel() < self.mingru_fold_floats(requests, max_q, width):
+                fold = None
+        self._check(self.lib.ullm_mingru(
+            _DT[out.dtype], _ptr(azg), azg.stride(0), a_off, x_off, g_off, _ptr(b_z), _ptr(b_x), _ptr(state),
+            state.stride(0), _ptr(cu_q), _ptr(req_slots), _ptr(token_req), _ptr(out), out.stride(0), float(out_scale),
+            requests, width, int(max_q), _ptr(fold), _stream()), "mingru")
+
+    def mingru_chunk(self) -> int:
+        """Portions longer than this many tokens take the chunked form when a scratch buffer is given."""
+        return int(self.lib.ullm_mingru_chunk())
+
+    def mingru_fold_floats(self, requests: int, max_q: int, width: int) -> int:
+        c = self.lib.ullm_mingru_chunk()
+        return 2 * requests * (-(-max_q // c)) * width
 
     # -- matrix memory (mLSTM) ----------------------------------------------------
     def mlstm_supported(self, heads: int, dim: int, vdim: int) -> bool:

@@ -240,7 +240,10 @@ class ModelRunner:
             h[o_req:o_req + B] = range(B)
             for g in range(len(cache.groups)):
                 o_sm = seg(f"slot_mapping{g}")
-                h[o_sm:o_sm + B] = [rc.pages[g][s // ps] * ps + s % ps for rc, s in zip(rcs, starts)]
+                if cache.groups[g].need.every > 1:
+                    h[o_sm:o_sm + B] = [cache.slot_of(rc, g, s) for rc, s in zip(rcs, starts)]
+                else:
+                    h[o_sm:o_sm + B] = [rc.pages[g][s // ps] * ps + s % ps for rc, s in zip(rcs, starts)]
             rows = [b for b, e in enumerate(entries) for _ in e.want]
             h[o_rows:o_rows + len(rows)] = rows
             h[o_kv:o_kv + B] = [s + 1 for s in starts]

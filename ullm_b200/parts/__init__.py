@@ -16,7 +16,7 @@ from .registry import (
     register_norm,
     register_position_encoding,
 )
-from . import norm, position, attention, mlp, moe, mlstm, gla, block  # noqa: F401  (register the built-in kinds)
+from . import norm, position, attention, window_attention, mingru, mlp, moe, mlstm, gla, block  # noqa: F401  (register the built-in kinds)
 from .model import DecoderModel
 
 __all__ = [

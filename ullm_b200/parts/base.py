@@ -47,16 +47,23 @@ class CacheNeed:
     """Keys and values this mixer keeps per token: `num_kv_heads` x `head_dim`
     for K and `num_kv_heads` x `value_dim` for V (None: `head_dim`).  `window`:
     None keeps every token, w keeps the last w, and with `keep_first` also the
-    first `keep_first` tokens of the request."""
+    first `keep_first` tokens of the request.  `values_in_keys`: there are no value
+    pages (the mixer reads its values out of the key rows).  `every` n > 1: the
+    cache holds one entry per n tokens (entry e is written when token (e + 1) n - 1
+    arrives), all of them kept; its pages are counted in entries."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     value_dim: int | None = None
     keep_first: int = 0
+    values_in_keys: bool = False
+    every: int = 1
 
     @property
     def v_dim(self) -> int:
+        if self.values_in_keys:
+            return 0
         return self.head_dim if self.value_dim is None else self.value_dim
 
 
@@ -124,6 +131,12 @@ class Norm(Part):
         """out[r] = norm(stream[rows[r]]) for a 32-bit stream (`rows` None: every row), rounded to out's dtype."""
         raise NotImplementedError
 
+    def row_params(self):
+        """(weight, eps, centred) if this norm is w * (x - mean) / sqrt(variance + eps) over the whole row (centred)
+        or w * x / sqrt(mean(x^2) + eps) (not centred), which a block may then hand to a kernel that norms a
+        sub-layer's output, adds it to the stream and applies the next norm at once; None otherwise."""
+        return None
+
     def rms_params(self):
         """(weight, eps) if this norm is a plain RMSNorm over the whole row, which a block may then fold into a
         fused kernel; None otherwise."""
@@ -159,6 +172,11 @@ class Mixer(Part):
         return None
 
     def state_need(self) -> StateNeed | None:
+        return None
+
+    def aux_cache_need(self) -> CacheNeed | None:
+        """A second cache of the same execution (pooled entries beside the tokens' pages, say); the mixer finds
+        it as `cache.aux` (pages, the group's step data)."""
         return None
 
     def graph_key(self, ctx):

@@ -12,7 +12,7 @@ import torch
 from ..csrc import kernels
 from .base import Block, ParamDecl
 from .linear import linear
-from .registry import register_block
+from .registry import build_norm, register_block
 
 
 @register_block("prenorm_residual")
@@ -339,5 +339,93 @@ class ParallelGatedBlock(Block):
                     ctx.prepared_norm = (next_norm, h_next)
             if not done:
                 K.norm_scale_add(y, stream, self.tensors[n["side_norm"]], self.eps, 1.0, None)
+        ctx.stream_operand = None
+        return None, stream
+
+
+@register_block("sandwich_residual")
+class SandwichResidualBlock(Block):
+    """A norm on BOTH sides of each sub-layer, on a 32-bit residual stream:
+
+        x <- x + norm_1b(mixer(norm_1(x)));   x <- x + norm_2b(feed_forward(norm_2(x)))
+
+    `mixer_norm` / `feed_forward_norm` are the norms in front, `mixer_out_norm` / `feed_forward_out_norm`
+    (`NormSpec`s among the block's arguments) the ones behind.  A layer may have no feed-forward (and then neither
+    of its norms).  The norms must offer `row_params()`: one kernel norms a sub-layer's output, adds it to the
+    stream and leaves the rows of the norm that reads the stream next (this block's second one, or the next
+    block's first, `ctx.prepared_norm`), so the stream is read and written once per sub-layer."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, names=None, mixer_out_norm=None,
+                 feed_forward_out_norm=None):
+        super().__init__()
+        if mixer_out_norm is None:
+            raise ValueError("this arrangement norms the mixer's output too (mixer_out_norm)")
+        if not ((feed_forward is None) == (feed_forward_norm is None) == (feed_forward_out_norm is None)):
+            raise ValueError("a feed-forward and its two norms come together or not at all")
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.mixer_out_norm = build_norm(mixer_out_norm)
+        self.feed_forward_out_norm = build_norm(feed_forward_out_norm) if feed_forward_out_norm is not None else None
+        for nm in (self.mixer_norm, self.mixer_out_norm, self.feed_forward_norm, self.feed_forward_out_norm):
+            if nm is not None and not hasattr(nm, "row_params"):
+                raise ValueError(f"{type(nm).__name__} cannot be folded into the stream's row kernels")
+        self.hidden_size = mixer_norm.size
+        n = dict(mixer="mixer.", feed_forward="feed_forward.", mixer_norm="mixer_norm.",
+                 mixer_out_norm="mixer_out_norm.", feed_forward_norm="feed_forward_norm.",
+                 feed_forward_out_norm="feed_forward_out_norm.")
+        n.update(names or {})
+        self.names = n
+
+    def subparts(self):
+        n = self.names
+        s = {n["mixer_norm"]: self.mixer_norm, n["mixer_out_norm"]: self.mixer_out_norm, n["mixer"]: self.mixer}
+        if self.feed_forward is not None:
+            s[n["feed_forward_norm"]] = self.feed_forward_norm
+            s[n["feed_forward_out_norm"]] = self.feed_forward_out_norm
+            s[n["feed_forward"]] = self.feed_forward
+        return s
+
+    def activation_elems(self):
+        ff = self.feed_forward.activation_elems() if self.feed_forward is not None else 0
+        return 3 * self.hidden_size + max(self.mixer.activation_elems(), ff)
+
+    takes_next_norm = True  # `forward` accepts the norm that the next block will apply first
+
+    def accepts_folded_norm(self) -> bool:
+        """True: this block can start from normed rows that whoever updated the stream last left in
+        `ctx.prepared_norm`."""
+        return self.mixer_norm.row_params() is not None
+
+    def forward(self, x, residual, ctx, cache, next_norm=None):
+        """The stream arrives as `x` (first block, residual None) or as `residual` (x None); returns (None, stream)."""
+        K = kernels()
+        stream = residual if residual is not None else x
+        if stream.dtype != torch.float32:
+            raise RuntimeError("this block takes a 32-bit residual stream (ModelSpec.stream_dtype='float32')")
+        T, W = stream.shape
+        ws = ctx.workspace
+        dt = self.mixer.operand_dtype()
+        prepared, ctx.prepared_norm = getattr(ctx, "prepared_norm", None), None
+        if prepared is not None and prepared[0] is self.mixer_norm and prepared[1].shape == (T, W):
+            h = prepared[1]
+        else:
+            h = ws.tokens("block.normed", T, W, dt)
+            self.mixer_norm.forward_rows(stream, None, h)
+        a = self.mixer.forward(h, ctx, cache)
+        nxt = next_norm.row_params() if (next_norm is not None and hasattr(next_norm, "row_params")) else None
+        if nxt is not None and nxt[0].numel() != W:
+            nxt = None
+        # (every reader of h is done when the kernel that overwrites it runs: the rows take its place)
+        h2 = ws.tokens("block.normed", T, W, dt)
+        w, eps, center = self.mixer_out_norm.row_params()
+        if self.feed_forward is not None:
+            K.norm_add_norm(stream, a, w, eps, 1.0, center, next_norm=(*self.feed_forward_norm.row_params(), h2))
+            f = self.feed_forward.forward(h2, ctx)
+            w, eps, center = self.feed_forward_out_norm.row_params()
+            K.norm_add_norm(stream, f, w, eps, 1.0, center, next_norm=(*nxt, h2) if nxt is not None else None)
+        else:
+            K.norm_add_norm(stream, a, w, eps, 1.0, center, next_norm=(*nxt, h2) if nxt is not None else None)
+        if nxt is not None:
+            ctx.prepared_norm = (next_norm, h2)
         ctx.stream_operand = None
         return None, stream

@@ -10,3 +10,15 @@ from ..csrc import kernels
 
 def linear(x, weight, out, bias=None):
     return kernels().linear(x, weight, out, bias)
+
+
+def batched_matmul(x, w, out):
+    """out[b] = x[b] @ w[b] for b in a batch of small independent products (one per head, say): x [B, T, k],
+    w [B, k, n], out [B, T, n], each with unit stride in one of its last two dimensions (views of wider rows are
+    fine).  The vendor library's strided batched product; in float32 without any reduced-precision mode."""
+    import torch
+
+    if not x.is_cuda:
+        raise RuntimeError("batched_matmul runs on CUDA tensors only (no CPU path)")
+    torch.bmm(x, w, out=out)
+    return out

@@ -66,3 +66,42 @@ class GatedMLP(FeedForward):
         out = ctx.workspace.tokens("ffn.out", T, self.hidden_size, x.dtype)
         linear(act, self.tensors[self.names["down"]], out)
         return out
+
+
+@register_feed_forward("dense_mlp")
+class DenseMLP(FeedForward):
+    """down(act(up(x))) without a gate.  Activations: "xielu", with two learned numbers (p, q) in the tensor
+    `act` [2]:
+
+        z > 0:   softplus(p) z^2 + z / 2
+        z <= 0:  (1/2 + softplus(q)) (e^z - 1 - z) + z / 2
+
+    evaluated in 32-bit on the product's rounded output (csrc/sandwich_norm.cu)."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "xielu", names: dict | None = None):
+        super().__init__()
+        if activation != "xielu":
+            raise ValueError(f"activation {activation!r} unknown (have ['xielu'])")
+        if hidden_size <= 0 or intermediate_size <= 0:
+            raise ValueError("sizes must be positive")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        n = dict(up="up_proj.weight", down="down_proj.weight", act="act")
+        n.update(names or {})
+        self.names = n
+
+    def param_decls(self):
+        H, I, n = self.hidden_size, self.intermediate_size, self.names
+        return {n["up"]: ParamDecl((I, H)), n["down"]: ParamDecl((H, I)), n["act"]: ParamDecl((2,), "bias32")}
+
+    def activation_elems(self):
+        return 2 * self.intermediate_size + self.hidden_size
+
+    def forward(self, x, ctx):
+        T, I, n = x.shape[0], self.intermediate_size, self.names
+        u = ctx.workspace.tokens("mlp.up", T, I, x.dtype)
+        linear(x, self.tensors[n["up"]], u)
+        a = ctx.workspace.tokens("mlp.act", T, I, x.dtype)
+        kernels().xielu(u, self.tensors[n["act"]], a)
+        out = ctx.workspace.tokens("ffn.out", T, self.hidden_size, x.dtype)
+        linear(a, self.tensors[n["down"]], out)
+        return out

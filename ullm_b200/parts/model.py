@@ -12,7 +12,7 @@ import torch
 
 from ..config.specs import ModelSpec
 from ..csrc import kernels
-from .base import Part
+from .base import ParamDecl, Part
 from .embedding import OutputHead, TokenEmbedding, TokenSideTable
 from .registry import build_block, build_norm, build_position_encoding
 
@@ -43,6 +43,7 @@ class DecoderModel(Part):
         if spec.token_side is not None:
             self.token_side = TokenSideTable(spec.vocab_size, spec.token_side.dim, spec.token_side.shares)
         self.schedule = list(spec.schedule)
+        self._keeps_input = any(e.add_input for e in self.schedule)
         # one mixer of each group answers `graph_key` for all of its kind
         seen: dict = {}
         for e in self.schedule:
@@ -62,13 +63,19 @@ class DecoderModel(Part):
             s[self.spec.token_side.name] = self.token_side
         return s
 
+    def param_decls(self):
+        if self.spec.pass_vectors is None:
+            return {}
+        name, rows = self.spec.pass_vectors
+        return {name: ParamDecl((rows, self.spec.hidden_size), "bias32")}
+
     # -- what the cache manager needs to know ------------------------------
     def cache_needs(self):
-        """Per schedule entry: (CacheNeed | None, StateNeed | None, cache_of)."""
+        """Per schedule entry: (CacheNeed | None, StateNeed | None, cache_of, second CacheNeed | None)."""
         out = []
         for e in self.schedule:
             m = self.blocks[e.layer].mixer
-            out.append((m.cache_need(), m.state_need(), e.cache_of))
+            out.append((m.cache_need(), m.state_need(), e.cache_of, m.aux_cache_need()))
         return out
 
     def graph_key(self, ctx) -> tuple:
@@ -107,13 +114,24 @@ class DecoderModel(Part):
         else:
             x = ctx.workspace.tokens("model.hidden", T, self.spec.hidden_size, self.dtype)
             self.embedding.forward(ctx.token_ids, x, ctx)
+        x0 = None
+        if self._keeps_input:
+            # the input as the embedding left it, for the executions that add it to the stream again
+            x0 = ctx.workspace.tokens("model.input", T, self.spec.hidden_size, torch.float32)
+            x0.copy_(x)
         residual = None
         n = len(self.schedule)
         for i, e in enumerate(self.schedule):
             block = self.blocks[e.layer]
+            if e.add_input or e.add_vector is not None:
+                self._add_to_stream(residual if residual is not None else x, x0 if e.add_input else None,
+                                    e.add_vector, block, ctx)
             if block.takes_next_norm:
                 # the norm that the next block applies first, if that block can start from what this one prepares
+                # (not when something is added to the stream in between: that addition prepares it then)
                 nxt = self.blocks[self.schedule[i + 1].layer] if i + 1 < n else None
+                if nxt is not None and (self.schedule[i + 1].add_input or self.schedule[i + 1].add_vector is not None):
+                    nxt = None
                 nxt_norm = nxt.mixer_norm if (nxt is not None and nxt.accepts_folded_norm()) else None
                 x, residual = block.forward(x, residual, ctx, caches[i], next_norm=nxt_norm)
             else:
@@ -121,6 +139,24 @@ class DecoderModel(Part):
         ctx.folded_norm = None
         ctx.prepared_norm = None
         return x, residual
+
+    def _add_to_stream(self, stream, rows, vector, block, ctx) -> None:
+        """stream += rows (if given) + row `vector` of the pass vectors (if given), in this order, in 32-bit; the
+        same kernel leaves the rows of the norm that `block` applies first, if it can start from them."""
+        if stream is None or stream.dtype != torch.float32:
+            raise RuntimeError("additions to the stream between layers need a 32-bit stream")
+        vec = self.tensors[self.spec.pass_vectors[0]][vector] if vector is not None else None
+        ctx.prepared_norm = None
+        nxt = None
+        if block.takes_next_norm and block.accepts_folded_norm() and hasattr(block.mixer_norm, "row_params"):
+            params = block.mixer_norm.row_params()
+            if params is not None and params[0].numel() == stream.shape[1]:
+                h = ctx.workspace.tokens("block.normed", stream.shape[0], stream.shape[1], block.mixer.operand_dtype())
+                nxt = (*params, h)
+        kernels().norm_add_norm(stream, extra_rows=rows, extra_vec=vec, next_norm=nxt)
+        if nxt is not None:
+            ctx.prepared_norm = (block.mixer_norm, nxt[3])
+        ctx.stream_operand = None
 
     def forward(self, ctx, caches):
         """Logits [len(ctx.logits_rows), vocab] float32 at the wanted rows."""

@@ -69,11 +69,13 @@ class ComputedRotaryPositions(PositionEncoding):
     """A rotation whose angles the mixer's kernel computes itself: `tables()` holds only `inv_freq`
     (rotary_dim / 2 floats, built in 64-bit, kept in 32-bit); the kernel forms the 32-bit product position x
     frequency and its sine and cosine, so there is no table per position and no largest position.  Dimension i of
-    a head is rotated with dimension i + rotary_dim / 2.  `scaling`: see `scaled_frequencies`."""
+    a head is rotated with dimension i + rotary_dim / 2, or with `interleaved` dimension 2i with 2i + 1 (the
+    mixer's kernel must know the pairing asked for: a mixer checks this flag).  `scaling`: see `scaled_frequencies`."""
 
     computed = True
 
-    def __init__(self, rotary_dim: int, theta: float, max_positions: int = 0, scaling: dict | None = None):
+    def __init__(self, rotary_dim: int, theta: float, max_positions: int = 0, scaling: dict | None = None,
+                 interleaved: bool = False):
         super().__init__()
         if rotary_dim <= 0 or rotary_dim % 2:
             raise ValueError(f"rotary_dim={rotary_dim} must be a positive even number")
@@ -83,6 +85,7 @@ class ComputedRotaryPositions(PositionEncoding):
         self.theta = float(theta)
         self.max_positions = max_positions
         self.scaling = dict(scaling) if scaling else None
+        self.interleaved = bool(interleaved)
         scaled_frequencies(rotary_dim, self.theta, self.scaling)  # (refuses bad constants now, not at load time)
         self._tables: dict[str, torch.Tensor] = {}
 
