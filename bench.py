@@ -742,6 +742,52 @@ def run_borosun(args) -> dict:
     return out
 
 
+# ---------------------------------------------------------------------------------------------------------
+# `--workload pidenex`: the Pidenex decoder beside the Ludalix decoder (the closest design the engine has: windowed
+# attention and a recurrent state on a 32-bit stream, norms on both sides of a sub-layer) at equal layer sizes
+# ---------------------------------------------------------------------------------------------------------
+def pidenex_config(width: int, heads: int, kv_heads: int, ff: int, window: int, state_heads: int, state_dim: int,
+                   state_vdim: int, groups: int, vocab: int, side: int, pool: int = 64, kv_rank: int = 384,
+                   q_rank: int = 768) -> dict:
+    """Eight layer runs per two groups, as many as `ludalix_dense_config` has layers: a parallel layer (biased
+    windowed attention beside a minGRU of the model's width), then a latent-attention and a pooled-window layer
+    that run twice, then the three kinds once more; every one with a dense feed-forward."""
+    grouped = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5)
+    par = dict(left=dict(grouped, mask=dict(size=window)), right=dict(width=state_heads * state_vdim), left_scale=0.6,
+               right_scale=1.1)
+    lat = dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=kv_rank, q_rank=q_rank, scale=192 ** -0.5,
+               mask=dict(size=window), rot=dict(dims=64, base=1e6))
+    att = dict(grouped, mask=dict(size=window, pool=pool))
+    mlp = dict(kind="dense", ff=ff)
+    kinds = [("parallel", par), ("latent_attention", lat), ("attention", att)]
+    layers = [dict(type=t, mixer=dict(m), mlp=dict(mlp)) for _ in range(groups) for t, m in kinds]
+    return dict(architecture="Pidenex", vocab=vocab, width=width, embedding=dict(scale=12.0), norm=dict(eps=1e-5),
+                layers=layers, loop=dict(start=1, stop=3, times=groups // 2 + 1), torch_dtype="bfloat16")
+
+
+def run_pidenex(args) -> dict:
+    """`--workload pidenex`: prefill (one prompt of 2,048 tokens) and decode (8 requests holding 2,048 tokens each)
+    of the Pidenex decoder at layer sizes that resemble a real model's, random weights, beside the Ludalix decoder
+    with dense feed-forwards at equal sizes and as many layers as the Pidenex model has layer runs; per kernel
+    group the device time of one eager step of each kind.  One JSON object; the default workload and its line are
+    untouched."""
+    T, B, ctx_len = PREFILL_TOKENS, args.batch, START_CONTEXT
+    out = {"workload": "pidenex", "prefill_tokens": T, "decode_batch": B, "decode_context": ctx_len,
+           "data": "synthetic", "dtype": "bf16", "peaks": peaks(), "sizes": {}}
+    names = [args.case] if args.case else list(BOROSUN_SIZES)
+    for name in names:
+        size = BOROSUN_SIZES[name]
+        out["sizes"][name] = {}
+        pid = pidenex_config(**size)
+        runs = len(pid["layers"]) + (pid["loop"]["times"] - 1) * (pid["loop"]["stop"] - pid["loop"]["start"])
+        for label, cfg, n in (("pidenex", pid, runs), ("ludalix_dense", ludalix_dense_config(**size), 4 * size["groups"])):
+            if args.only_model and args.only_model != label:
+                continue
+            out["sizes"][name][label] = dict(_measure_model(cfg, False, T, B, ctx_len, args.steps, args.warmup),
+                                             layer_runs=n)
+    return out
+
+
 def run_extra_shapes(args, impl: str) -> dict:
     """The two further workloads, each in a process of its own (the 32B shape needs the device to itself), as
     flat entries for `points`."""
@@ -1404,7 +1450,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", default="8b", choices=["8b", "32b", "serve-0.6b", "8b-long", "ludalix", "borosun"],
+    ap.add_argument("--workload", default="8b", choices=["8b", "32b", "serve-0.6b", "8b-long", "ludalix", "borosun", "pidenex"],
                     help="8b: the default line (Qwen3-8B layer sizes); 32b: the same at Qwen3-32B layer sizes; "
                          "serve-0.6b: 256 requests under continuous batching at Qwen3-0.6B layer sizes; 8b-long: "
                          "prefill of 16,384 tokens and decode of 8 requests at that context")
@@ -1418,7 +1464,7 @@ def main() -> int:
                     help="--probe linear: launch only this kernel, eagerly, --steps times (for a profiler)")
     ap.add_argument("--shape", default="gate_up", choices=["qkv", "o", "gate_up", "down", "head"],
                     help="--probe linear --only: which of the decode step's products")
-    ap.add_argument("--only-model", default=None, help="--workload borosun: measure only this model (borosun, ludalix_dense)")
+    ap.add_argument("--only-model", default=None, help="--workload borosun / pidenex: measure only this model (borosun or pidenex, ludalix_dense)")
     ap.add_argument("--case", default=None, help="run only the case of this name (--probe prefill-attention, decode-attention)")
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens each request holds (--probe)")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens of a page (--probe decode-attention)")
@@ -1460,6 +1506,9 @@ def main() -> int:
         return 0
     if args.workload == "borosun":
         print(json.dumps(run_borosun(args)))
+        return 0
+    if args.workload == "pidenex":
+        print(json.dumps(run_pidenex(args)))
         return 0
     out = run_serve(args) if args.workload == "serve-0.6b" else run_ours(args)
     if extra:

@@ -56,13 +56,21 @@ def rotate_pairs(v, positions, dims, base):
 # ---------------------------------------------------------------------------------------------------------
 # attention cores (scores in a loop over query positions: slow and plain)
 # ---------------------------------------------------------------------------------------------------------
+def mask_of(m):
+    """(window size or None, pool or 0) of a mixer's configuration."""
+    mk = m.get("mask")
+    return (None, 0) if mk is None else (mk["size"], int(mk.get("pool") or 0))
+
+
 def window_attention(q, k, v, scale, size, slopes=None, pool=0):
-    """q [H, n, d], k [G, n, d], v [G, n, dv] -> [n, H * dv].  Query i sees j with 0 <= i - j < size; with `pool`
+    """q [H, n, d], k [G, n, d], v [G, n, dv] -> [n, H * dv].  Query i sees j with 0 <= i - j < size (None: every
+    j <= i); with `pool`
     P > 0 also one mean key / value per block of P positions that ends at or before i - size; with `slopes` [H]
     the score of (i, j) loses slopes[h] * (i - j).  One softmax over everything a query sees."""
     H, n, _ = q.shape
     G, dv = k.shape[0], v.shape[-1]
     rep = H // G
+    size = n + 1 if size is None else size
     out = torch.zeros(n, H, dv, dtype=q.dtype)
     if pool:
         nb = n // pool
@@ -101,13 +109,16 @@ def latent_attention(h, m, w, pre, eps):
     q = (cq @ w[pre + "uq"].T).reshape(n, H, d + r).transpose(0, 1)  # [H, n, d + r]
     dkv = h @ w[pre + "dkv"].T
     c = rms_norm(dkv[:, :R], w[pre + "dkv.norm"], eps)
+    if not r:
+        m = dict(m, rot=dict(dims=0, base=1.0))
     k_rot = rotate_pairs(dkv[:, R:], pos, m["rot"]["dims"], m["rot"]["base"])  # [n, r]
     k_plain = (c @ w[pre + "uk"].T).reshape(n, H, d).transpose(0, 1)
     v = (c @ w[pre + "uv"].T).reshape(n, H, dv).transpose(0, 1)
     q_rot = rotate_pairs(q[..., d:], pos, m["rot"]["dims"], m["rot"]["base"])
     qq = torch.cat([q[..., :d], q_rot], -1)
     kk = torch.cat([k_plain, k_rot[None].expand(H, n, r)], -1)
-    o = window_attention(qq, kk, v, m["scale"], m["mask"]["size"])
+    size, pool = mask_of(m)
+    o = window_attention(qq, kk, v, m["scale"], size, pool=pool)
     return o @ w[pre + "o"].T
 
 
@@ -117,7 +128,8 @@ def pooled_attention(h, m, w, pre):
     H, G, d = m["heads"], m["kv_heads"], m["dim"]
     q = (h @ w[pre + "q"].T).reshape(n, H, d).transpose(0, 1)
     k = (h @ w[pre + "k"].T).reshape(n, G, d).transpose(0, 1)
-    o = window_attention(q, k, k, m["scale"], m["mask"]["size"], pool=int(m["mask"].get("pool") or 0))
+    size, pool = mask_of(m)
+    o = window_attention(q, k, k, m["scale"], size, pool=pool)
     return o @ w[pre + "o"].T
 
 
@@ -130,7 +142,7 @@ def biased_attention_unprojected(h, m, w, pre, eps):
     v = k_flat.reshape(n, G, d).transpose(0, 1)
     q = rms_norm(q_flat, w[pre + "q.norm"], eps).reshape(n, H, d).transpose(0, 1)
     k = rms_norm(k_flat, w[pre + "k.norm"], eps).reshape(n, G, d).transpose(0, 1)
-    o = window_attention(q, k, v, m["scale"], m["mask"]["size"], slopes=head_slopes(H, h.dtype))
+    o = window_attention(q, k, v, m["scale"], mask_of(m)[0], slopes=head_slopes(H, h.dtype))
     return o * torch.sigmoid(h @ w[pre + "g"].T)
 
 
