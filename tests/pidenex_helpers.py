@@ -113,3 +113,15 @@ def make_runner(tmp_path, cfg, w, page, dtype, num_pages=64, max_requests=4, nam
 def oracle(ids, w, cfg) -> torch.Tensor:
     """Logits at every position, 64-bit arithmetic on the weights as given (rounded ones stay rounded)."""
     return pp.forward(cfg, {n: t.double() for n, t in w.items()}, ids).float()
+
+
+# E: sizes the tensor-core attention kernel of the 16-bit path takes (rows of 16-byte multiples): grouped heads of
+# 64 and 128 with windows longer than a key tile, blocks of 8 behind one of them, a latent whose key row (56 + 16)
+# is no multiple of 16 while its rank is, values wider than one pass of the kernel (160 > 128)
+CFG_E = config(96, 150, [
+    ("parallel", parallel(4, 2, 64, 0.125, 70, 48, 0.8, 0.9), dense(72)),
+    ("attention", attention(4, 1, 128, 0.09, 40, pool=8), None),
+    ("latent_attention", latent(4, 32, 16, 24, 56, 48, 0.15, 90), dense(64)),
+    ("latent_attention", latent(2, 16, 16, 40, 160, 32, 0.2, 33, base=500.0), None),
+], loop=(1, 3, 2))
+CONFIGS["E"] = (CFG_E, 16)

@@ -156,6 +156,9 @@ class Kernels:
         # attention with capped scores or mixed heads (the general path of parts/attention.py) on the tensor-core
         # kernels where the sizes allow; 0: the general kernel always
         self.general_attention_tc = get("ULLM_B200_GENERAL_ATTN_TC", "1") != "0"
+        # windowed attention with its further options (values inside the keys, slopes, pooled blocks, a gate) on the
+        # tensor-core kernel of csrc/attention_window.cu where the sizes allow; 0: the general kernel always
+        self.window_attention_tc = get("ULLM_B200_WINDOW_ATTN_TC", "1") != "0"
         # the splits of a request's keys merge inside a thread-block cluster (at most 8 splits) instead of through
         # scratch arrays and a second kernel
         # ("auto": for steps of at most 8 rows; "1" / "0": always / never, with `decode_split_target` splits)
@@ -256,6 +259,8 @@ class Kernels:
             "ullm_paged_attention_generic_ex2": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P, I, I,
                                                  F, P],
             "ullm_mix_heads": [I, P, P, P, I, I, I, I, P],
+            "ullm_window_attention": [P, LL, P, LL, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, LL, P, P, P, I, P, P,
+                                      P, I, LL, P, LL, F],
             "ullm_paged_attention_generic_ex3": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P, I, I,
                                                  F, P, I, I, P, P, P, I, LL, P, LL, F, LL],
             "ullm_norm_add_norm": [I, P, P, P, I, I, F, F, I, P, P, P, F, I, I, P, P],
@@ -314,6 +319,8 @@ class Kernels:
         L.ullm_lt_available.restype = c_int
         L.ullm_lt_last_choice.argtypes = [P, P, P, P]
         L.ullm_lt_last_choice.restype = None
+        L.ullm_window_attention_supported.argtypes = [I, I, I, I, I]
+        L.ullm_window_attention_supported.restype = c_int
         L.ullm_prefill_attention_supported.argtypes = [I, I, I]
         L.ullm_prefill_attention_supported.restype = c_int
         L.ullm_prefill_attention_tcgen05_supported.argtypes = [I, I, I, I]
@@ -983,8 +990,11 @@ class Kernels:
     @_timed("attention")
     def windowed_attention(self, q, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req, num_q: int,
                            num_kv: int, head_dim: int, v_dim: int, page_size: int, window: int, scale: float, *,
-                           slopes=None, pool: int = 0, pooled=None, gate=None, out_scale: float = 1.0):
-        """The general attention kernel with its further options.  `v_pages` None: a head's values are the first
+                           slopes=None, pool: int = 0, pooled=None, gate=None, out_scale: float = 1.0,
+                           num_requests: int | None = None):
+        """Windowed attention with its further options: in bfloat16, at sizes `ullm_window_attention_supported`
+        takes and with `num_requests` (the batch rows that `cu_q` describes) given, the tensor-core kernel of
+        csrc/attention_window.cu; otherwise (32-bit storage, other sizes) the general kernel.  `v_pages` None: a head's values are the first
         `v_dim` elements of its key rows.  `slopes` (float32 [num_q]): score(i, j) -= slopes[h] (i - j).  `pool` P
         with `pooled` = (pooled key pages, pooled value pages or None, their block table): blocks of P positions
         that lie wholly before the window are seen through one mean key / value each.  `gate` [T, num_q x v_dim]
@@ -1023,6 +1033,20 @@ class Kernels:
             _need(gate, "gate", q.dtype, contiguous=False)
             if gate.stride(1) != 1 or gate.shape != (T, num_q * v_dim):
                 raise KernelError(f"windowed_attention: gate {tuple(gate.shape)}")
+        num_pages = k_pages.numel() // (page_size * num_kv * head_dim)
+        p_pages = pk.numel() // (page_size * num_kv * head_dim) if pk is not None else 0
+        if (self.window_attention_tc and q.dtype == torch.bfloat16 and num_requests and q.stride(0) % 8 == 0
+                and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0 and q.data_ptr() % 16 == 0
+                and self.lib.ullm_window_attention_supported(head_dim, v_dim, num_q, num_kv, int(v_pages is None))):
+            self.attention_path = "window_mma"
+            self._check(self.lib.ullm_window_attention(
+                _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+                block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, int(num_requests), num_q, num_kv,
+                head_dim, v_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream(),
+                _ptr(slopes), int(pool), _ptr(pk), _ptr(pv), _ptr(pbt), pbt.shape[1] if pbt is not None else 0, p_pages,
+                _ptr(gate), gate.stride(0) if gate is not None else 0, float(out_scale)),
+                f"window_attention (key rows {head_dim}, values {v_dim}, pool {pool})")
+            return
         self.attention_path = "generic"
         self._check(self.lib.ullm_paged_attention_generic_ex3(
             _DT[q.dtype], _ptr(q), q.stride(0), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
