@@ -49,6 +49,11 @@ struct WinArgs {
   long long gate_stride;
   float out_scale;
   int* status;
+  // nsplit > 1: the block's key tiles are cut into nsplit runs, one block each (grid.y); a block leaves its
+  // unnormalised 32-bit accumulator, maximum (in units of log2) and sum in `parts`
+  // [token x head][nsplit][dv + 2], and `window_merge_kernel` forms the output rows
+  int nsplit;
+  float* parts;
 };
 
 __device__ __forceinline__ void win_cp_async_16(void* smem, const void* gmem, bool pred) {
@@ -139,6 +144,15 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
   const int ntok = min(tpt, q_len - first);
   const int rows_valid = ntok * G;
   const int p0 = kvl - q_len + first, p1 = p0 + ntok - 1;  // positions of this block's tokens
+  const int nsplit = a.nsplit, split = blockIdx.y;
+  if ((kvl <= 0 || p0 < 0) && nsplit > 1) {  // padding request: nothing seen, the merge writes zeros
+    for (int row = tid; row < rows_valid; row += THREADS) {
+      float* pp = a.parts + (((long long)(q_begin + first + row / G) * a.num_q + kh * G + row % G) * nsplit + split) * (dv + 2);
+      pp[dv] = -INFINITY;
+      pp[dv + 1] = 0.f;
+    }
+    return;
+  }
   if (kvl <= 0 || p0 < 0) {                                // padding request: zeros
     for (int i = tid; i < rows_valid * dv; i += THREADS) {
       const int row = i / dv, d = i - row * dv;
@@ -151,6 +165,8 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
   const int nb = (W > 0 && a.pool > 0 && p1 - W + 1 > 0) ? (p1 - W + 1) / a.pool : 0;  // pooled entries in sight
   const int ptiles = (nb + WIN_N - 1) / WIN_N;
   const int tiles = ptiles + (p1 - key0 + WIN_N) / WIN_N;
+  const int per_split = (tiles + nsplit - 1) / nsplit;
+  const int t_begin = min(tiles, split * per_split), t_end = min(tiles, t_begin + per_split);
   const int* bt = a.block_table + (long long)a.req_slots[r] * a.max_pages;
   const int* pbt = nb > 0 ? a.p_block_table + (long long)a.req_slots[r] * a.p_max_pages : nullptr;
   const long long kv_row = (long long)num_kv * dk, v_row = (long long)num_kv * dv;
@@ -229,10 +245,10 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
 #pragma unroll
   for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
-  issue(0);
+  if (t_begin < t_end) issue(t_begin);
   win_commit();
-  for (int it = 0; it < tiles; ++it) {
-    if (it + 1 < tiles) issue(it + 1);
+  for (int it = t_begin; it < t_end; ++it) {
+    if (it + 1 < t_end) issue(it + 1);
     win_commit();
     win_wait<1>();
     __syncthreads();
@@ -351,7 +367,16 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
     ls += __shfl_xor_sync(0xffffffffu, ls, 2);
     const float inv = (ls > 0.f ? 1.f / ls : 0.f) * out_scale;
     const int row = wrow + (lane >> 2) + h * 8;
-    if (row < rows_valid) {
+    if (row < rows_valid && nsplit > 1) {
+      float* pp = a.parts + (((long long)(q_begin + first + row / G) * a.num_q + kh * G + row % G) * nsplit + split) * (dv + 2);
+#pragma unroll
+      for (int j = 0; j < NT_O; ++j)
+        if (c0 + j * 8 < dv) *reinterpret_cast<float2*>(pp + c0 + j * 8 + c) = make_float2(o[j][2 * h], o[j][2 * h + 1]);
+      if (cw == 0 && (lane & 3) == 0) {
+        pp[dv] = m[h];
+        pp[dv + 1] = ls;
+      }
+    } else if (row < rows_valid) {
       const long long tok = q_begin + first + row / G;
       const long long col = (long long)(kh * G + row % G) * dv + c0 + c;
       __nv_bfloat16* op = a.out + tok * a.out_stride + col;
@@ -371,7 +396,47 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
   }
 }
 
+// One block per (token, head): the splits' accumulators, weighted by 2^(m_s - max m), over the weighted sums;
+// then the scale, the gate and the one rounding.
+__global__ void __launch_bounds__(128) window_merge_kernel(const WinArgs a) {
+  __shared__ float w_s[64];
+  __shared__ float inv_s;
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long th = blockIdx.x;
+  const int dv = a.dv, nsplit = a.nsplit, tid = threadIdx.x;
+  const float* pp = a.parts + th * nsplit * (dv + 2);
+  if (tid < 32) {
+    float mx = -INFINITY;
+    for (int s = tid; s < nsplit; s += 32) mx = fmaxf(mx, pp[(long long)s * (dv + 2) + dv]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int s = tid; s < nsplit; s += 32) {
+      const float ms = pp[(long long)s * (dv + 2) + dv];
+      const float w = ms == -INFINITY ? 0.f : win_ex2(ms - mx);
+      w_s[s] = w;
+      sum += w * pp[(long long)s * (dv + 2) + dv + 1];
+    }
+    sum = warp_sum(sum);
+    if (tid == 0) inv_s = (sum > 0.f ? 1.f / sum : 0.f) * (a.out_scale != 0.f ? a.out_scale : 1.f);
+  }
+  __syncthreads();
+  const long long tok = th / a.num_q;
+  const int head = (int)(th - tok * a.num_q);
+  __nv_bfloat16* op = a.out + tok * a.out_stride + (long long)head * dv;
+  const __nv_bfloat16* gp = a.gate != nullptr ? a.gate + tok * a.gate_stride + (long long)head * dv : nullptr;
+  for (int e = tid; e < dv; e += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < nsplit; ++s)
+      if (w_s[s] > 0.f) acc += w_s[s] * pp[(long long)s * (dv + 2) + e];
+    acc *= inv_s;
+    if (gp != nullptr) acc /= 1.f + expf(-__bfloat162float(gp[e]));
+    op[e] = __float2bfloat16_rn(acc);
+  }
+}
+
 #define WIN_SMEM_LIMIT (227 * 1024)
+#define WIN_MAX_SPLITS 64
 
 template <int DVW, int CW>
 static int launch_window(const WinArgs& a, int tokens, long long smem, cudaStream_t st) {
@@ -388,8 +453,10 @@ static int launch_window(const WinArgs& a, int tokens, long long smem, cudaStrea
   // at most ceil(tokens / tpt) + num_requests token tiles exist, however the tokens are spread
   const long long blocks = ((long long)(tokens + tpt - 1) / tpt + a.num_requests) * a.num_kv;
   if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
-  return ullm_launch_kernel(window_attention_kernel<DVW, CW>, dim3((unsigned)blocks), dim3(WIN_RW * CW * 32),
-                            (size_t)smem, st, a);
+  const int rc = ullm_launch_kernel(window_attention_kernel<DVW, CW>, dim3((unsigned)blocks, (unsigned)a.nsplit),
+                                    dim3(WIN_RW * CW * 32), (size_t)smem, st, a);
+  if (rc != ULLM_OK || a.nsplit <= 1) return rc;
+  return ullm_launch_kernel(window_merge_kernel, dim3((unsigned)((long long)tokens * a.num_q)), dim3(128), 0, st, a);
 }
 
 // Sizes this kernel takes (bfloat16): key rows and values multiples of 16, values up to 512, at most 64 query
@@ -403,6 +470,8 @@ extern "C" int ullm_window_attention_supported(int dk, int dv, int num_q, int nu
 
 // `v_cache` null: values inside the key rows (and then `pv` null too).  `slopes` (32-bit [num_q]) or null;
 // `pool` > 0 with the pooled pages `pk` (`pv`) and their block table; `gate` or null; `out_scale` 0 = 1.
+// `nsplit` > 1 (at most 64) with `parts` (32-bit, tokens x num_q x nsplit x (dv + 2)): a block's key tiles are
+// cut into nsplit runs that run side by side and are merged by a second launch (steps of few rows).
 // q rows, page rows, `out` and `gate` rows must start on 16- (q, pages) and 4-byte (out) boundaries.
 extern "C" int ullm_window_attention(const void* q, long long q_row_stride, void* out, long long out_stride,
                                      const void* k_cache, const void* v_cache, const int* block_table, int max_pages,
@@ -411,7 +480,7 @@ extern "C" int ullm_window_attention(const void* q, long long q_row_stride, void
                                      float scale, long long num_pages, int* status, void* stream, const float* slopes,
                                      int pool, const void* pk, const void* pv, const int* p_block_table,
                                      int p_max_pages, long long p_num_pages, const void* gate, long long gate_stride,
-                                     float out_scale) {
+                                     float out_scale, int nsplit, float* parts) {
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens < 0 || num_requests <= 0 || page_size <= 0 || max_pages <= 0 || window < 0 || pool < 0)
     return ULLM_ERR_BAD_SIZE;
@@ -422,6 +491,9 @@ extern "C" int ullm_window_attention(const void* q, long long q_row_stride, void
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)pk | (uintptr_t)pv) & 15) return ULLM_ERR_BAD_SIZE;
   if (q_row_stride % 8 || ((uintptr_t)out & 3) || out_stride % 2 || out_stride < (long long)num_q * dv)
     return ULLM_ERR_BAD_SIZE;
+  if (nsplit < 1 || nsplit > WIN_MAX_SPLITS || (nsplit > 1 && parts == nullptr) || ((uintptr_t)parts & 7))
+    return ULLM_ERR_BAD_SIZE;
+  if ((long long)tokens * num_q > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
   if (tokens == 0) return ULLM_OK;
   WinArgs a = {};
   a.q = (const __nv_bfloat16*)q;
@@ -455,6 +527,8 @@ extern "C" int ullm_window_attention(const void* q, long long q_row_stride, void
   a.gate_stride = gate_stride;
   a.out_scale = out_scale;
   a.status = status;
+  a.nsplit = nsplit;
+  a.parts = parts;
   const long long smem = win_smem_bytes(dk, dv, v_cache != nullptr);
   if (dv <= 64) return launch_window<64, 1>(a, tokens, smem, st);
   if (dv <= 128) return launch_window<128, 1>(a, tokens, smem, st);

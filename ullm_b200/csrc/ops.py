@@ -260,7 +260,7 @@ class Kernels:
                                                  F, P],
             "ullm_mix_heads": [I, P, P, P, I, I, I, I, P],
             "ullm_window_attention": [P, LL, P, LL, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, LL, P, P, P, I, P, P,
-                                      P, I, LL, P, LL, F],
+                                      P, I, LL, P, LL, F, I, P],
             "ullm_paged_attention_generic_ex3": [I, P, LL, P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, F, LL, P, P, I, I,
                                                  F, P, I, I, P, P, P, I, LL, P, LL, F, LL],
             "ullm_norm_add_norm": [I, P, P, P, I, I, F, F, I, P, P, P, F, I, I, P, P],
@@ -991,10 +991,11 @@ class Kernels:
     def windowed_attention(self, q, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req, num_q: int,
                            num_kv: int, head_dim: int, v_dim: int, page_size: int, window: int, scale: float, *,
                            slopes=None, pool: int = 0, pooled=None, gate=None, out_scale: float = 1.0,
-                           num_requests: int | None = None):
+                           num_requests: int | None = None, workspace=None):
         """Windowed attention with its further options: in bfloat16, at sizes `ullm_window_attention_supported`
         takes and with `num_requests` (the batch rows that `cu_q` describes) given, the tensor-core kernel of
-        csrc/attention_window.cu; otherwise (32-bit storage, other sizes) the general kernel.  `v_pages` None: a head's values are the first
+        csrc/attention_window.cu; otherwise (32-bit storage, other sizes) the general kernel.  With a `workspace`
+        a step of few rows cuts every row's keys into runs that run side by side (`_window_splits`).  `v_pages` None: a head's values are the first
         `v_dim` elements of its key rows.  `slopes` (float32 [num_q]): score(i, j) -= slopes[h] (i - j).  `pool` P
         with `pooled` = (pooled key pages, pooled value pages or None, their block table): blocks of P positions
         that lie wholly before the window are seen through one mean key / value each.  `gate` [T, num_q x v_dim]
@@ -1039,12 +1040,18 @@ class Kernels:
                 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0 and q.data_ptr() % 16 == 0
                 and self.lib.ullm_window_attention_supported(head_dim, v_dim, num_q, num_kv, int(v_pages is None))):
             self.attention_path = "window_mma"
+            splits = self._window_splits(T, int(num_requests), num_q, num_kv, int(window)) if workspace is not None else 1
+            parts = None
+            if splits > 1:
+                # (rows x splits <= 64 x blocks x splits < 64 x 2.5 x SMs whenever `_window_splits` splits)
+                parts = workspace.get("attn.window_parts", T * num_q * splits, v_dim + 2, torch.float32,
+                                      reserve=64 * 3 * self.sm_count)
             self._check(self.lib.ullm_window_attention(
                 _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
                 block_table.shape[1], _ptr(req_slots), _ptr(cu_q), _ptr(kv_len), T, int(num_requests), num_q, num_kv,
                 head_dim, v_dim, page_size, int(window), float(scale), num_pages, _ptr(self.status), _stream(),
                 _ptr(slopes), int(pool), _ptr(pk), _ptr(pv), _ptr(pbt), pbt.shape[1] if pbt is not None else 0, p_pages,
-                _ptr(gate), gate.stride(0) if gate is not None else 0, float(out_scale)),
+                _ptr(gate), gate.stride(0) if gate is not None else 0, float(out_scale), splits, _ptr(parts)),
                 f"window_attention (key rows {head_dim}, values {v_dim}, pool {pool})")
             return
         self.attention_path = "generic"
@@ -1057,6 +1064,17 @@ class Kernels:
             pk.numel() // (page_size * num_kv * head_dim) if pk is not None else 0, _ptr(gate),
             gate.stride(0) if gate is not None else 0, float(out_scale), out.stride(0)),
             f"windowed_attention (head_dim {head_dim}, values {v_dim}, pool {pool})")
+
+    def _window_splits(self, T: int, requests: int, num_q: int, num_kv: int, window: int) -> int:
+        """Into how many runs `windowed_attention` cuts a row's key tiles: one while the step's blocks (64 rows of
+        a kv head each) fill half of the SMs; otherwise as many as bring two blocks per SM, at most one run per
+        key tile of the window (32 without a window) and 64."""
+        tokens_per_block = max(1, 64 // (num_q // num_kv))
+        blocks = (max(requests, -(-T // tokens_per_block))) * num_kv
+        if 2 * blocks >= self.sm_count:
+            return 1
+        most = -(-window // 64) + 1 if window > 0 else 32
+        return max(1, min(-(-2 * self.sm_count // blocks), most, 64))
 
     # -- minGRU -------------------------------------------------------------------
     @_timed("mingru")

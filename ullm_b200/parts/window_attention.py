@@ -162,7 +162,7 @@ class KVSharedAttention(Mixer, _ProjectsOutput):
                              ctx.token_req, self.num_heads, self.num_kv_heads, self.head_dim, self.head_dim,
                              g.page_size, self.window or 0, self.scale, slopes=self.slopes, pool=self.pool,
                              pooled=pooled, gate=qk[:, q + kv:] if self.gated else None, out_scale=out_scale,
-                             num_requests=ctx.num_requests)
+                             num_requests=ctx.num_requests, workspace=ws)
         if not project_output:
             return attn
         res = ws.tokens("mixer.out", T, self.hidden_size, x.dtype)
@@ -272,7 +272,7 @@ class LatentAttention(Mixer):
         o_lat = ws.tokens("lat.o_lat", T, N * R, dt)
         K.windowed_attention(q_out, o_lat, cache.k_pages, None, g.block_table, g.req_slots, ctx.cu_q, g.kv_len,
                              ctx.token_req, N, 1, self.key_row, R, g.page_size, self.window or 0, self.scale,
-                             pool=self.pool, pooled=pooled, num_requests=ctx.num_requests)
+                             pool=self.pool, pooled=pooled, num_requests=ctx.num_requests, workspace=ws)
         # each head's latent output through its value up-projection: [heads, T, rank] x [heads, rank, vdim]
         attn = ws.tokens("attn.out", T, N * dv, dt)
         batched_matmul(o_lat.view(T, N, R).transpose(0, 1), self.tensors[n["uv"]].view(N, dv, R).transpose(1, 2),
