@@ -19,9 +19,8 @@
 // to its last token.  All stretches share one online softmax.
 #include "common.cuh"
 
-#define WIN_RW 4
-#define WIN_M (WIN_RW * 16)
 #define WIN_N 64
+#define WIN_MAX_GROUP 64  // query heads per kv head: a token's heads lie in one block
 
 struct WinArgs {
   const __nv_bfloat16* q;
@@ -54,6 +53,7 @@ struct WinArgs {
   // [token x head][nsplit][dv + 2], and `window_merge_kernel` forms the output rows
   int nsplit;
   float* parts;
+  int ksplit;  // the column groups of a row group share the steps of Q K^T (needs the exchange buffer)
 };
 
 __device__ __forceinline__ void win_cp_async_16(void* smem, const void* gmem, bool pred) {
@@ -95,19 +95,27 @@ __device__ __forceinline__ unsigned win_pack(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
+// values up to 128 wide: one column group; wider: two.  Four row groups (with eight, 256 threads of about 170
+// registers leave one block per SM; four leave three)
+static inline int win_row_groups(int dv) { return 4; }
+static inline int win_col_groups(int dv) { return dv <= 128 ? 1 : 2; }
 static inline long long win_smem_bytes(int dk, int dv, bool v_own) {
   const long long qs = dk * 2 + 16, vs = dv * 2 + 16;
-  return (long long)WIN_M * qs + 2LL * WIN_N * qs + (v_own ? 2LL * WIN_N * vs : 0) + 2LL * WIN_N * 8;
+  return 16LL * win_row_groups(dv) * qs + 2LL * WIN_N * qs + (v_own ? 2LL * WIN_N * vs : 0) + 2LL * WIN_N * 8;
+}
+// the partial scores that the column groups of a row group exchange: [row group][column group][32 registers][lane]
+static inline long long win_exchange_bytes(int dv) {
+  return win_col_groups(dv) > 1 ? 4096LL * win_row_groups(dv) * win_col_groups(dv) : 0;
 }
 
-template <int DVW, int CW>
-__global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(const WinArgs a) {
+template <int DVW, int CW, int RW>
+__global__ void __launch_bounds__(RW * CW * 32) window_attention_kernel(const WinArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int NT_S = WIN_N / 8, NT_O = DVW / 8, THREADS = WIN_RW * CW * 32;
+  constexpr int NT_S = WIN_N / 8, NT_O = DVW / 8, THREADS = RW * CW * 32, WIN_M = RW * 16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int rw = warp % WIN_RW, cw = warp / WIN_RW;
+  const int rw = warp % RW, cw = warp / RW;
   const int dk = a.dk, dv = a.dv, W = a.window, page_size = a.page_size;
   const bool v_own = a.v_cache != nullptr;
   const int qs = dk * 2 + 16;               // bytes between rows of the Q and K tiles
@@ -116,6 +124,7 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
   unsigned char* k_s = q_s + WIN_M * qs;
   unsigned char* v_s = k_s + 2 * WIN_N * qs;
   long long* slot_s = reinterpret_cast<long long*>(v_s + (v_own ? 2 * WIN_N * vs : 0));
+  float* exch_s = reinterpret_cast<float*>(slot_s + 2 * WIN_N);  // only with `ksplit`
 
   // consecutive blocks are the same token tile of all kv heads, the last tiles (most keys) first
   const int num_kv = a.num_kv;
@@ -181,6 +190,8 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
   }
   win_commit();
 
+  const int k_row0 = tid / kchunks, k_ch0 = tid % kchunks, k_drow = THREADS / kchunks, k_dch = THREADS % kchunks;
+  const int v_row0 = tid / vchunks, v_ch0 = tid % vchunks, v_drow = THREADS / vchunks, v_dch = THREADS % vchunks;
   auto issue = [&](int tile) {
     const int st = tile & 1;
     unsigned char* kbuf = k_s + st * WIN_N * qs;
@@ -198,20 +209,31 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
       slots[tid] = s;
     }
     __syncthreads();
-    const __nv_bfloat16* kc = pooled ? a.pk : a.k_cache;
-    for (int c = tid; c < WIN_N * kchunks; c += THREADS) {
-      const int row = c / kchunks, ch = c - row * kchunks;
+    // a thread's 16-byte pieces are THREADS apart: (row, piece) steps by the quotient and remainder found once
+    const __nv_bfloat16* kc = (pooled ? a.pk : a.k_cache) + (long long)kh * dk;
+    for (int row = k_row0, ch = k_ch0; row < WIN_N;) {
       const long long s = slots[row];
       const bool ok = s >= 0;
-      win_cp_async_16(kbuf + row * qs + ch * 16, kc + (ok ? s * kv_row + (long long)kh * dk + ch * 8 : 0), ok);
+      win_cp_async_16(kbuf + row * qs + ch * 16, kc + (ok ? s * kv_row + ch * 8 : 0), ok);
+      row += k_drow;
+      ch += k_dch;
+      if (ch >= kchunks) {
+        ch -= kchunks;
+        ++row;
+      }
     }
     if (v_own) {
-      const __nv_bfloat16* vc = pooled ? a.pv : a.v_cache;
-      for (int c = tid; c < WIN_N * vchunks; c += THREADS) {
-        const int row = c / vchunks, ch = c - row * vchunks;
+      const __nv_bfloat16* vc = (pooled ? a.pv : a.v_cache) + (long long)kh * dv;
+      for (int row = v_row0, ch = v_ch0; row < WIN_N;) {
         const long long s = slots[row];
         const bool ok = s >= 0;
-        win_cp_async_16(vbuf + row * vs + ch * 16, vc + (ok ? s * v_row + (long long)kh * dv + ch * 8 : 0), ok);
+        win_cp_async_16(vbuf + row * vs + ch * 16, vc + (ok ? s * v_row + ch * 8 : 0), ok);
+        row += v_drow;
+        ch += v_dch;
+        if (ch >= vchunks) {
+          ch -= vchunks;
+          ++row;
+        }
       }
     }
   };
@@ -220,7 +242,7 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
   const int wrow = rw * 16;
   const float log2e = 1.4426950408889634f;
   int pos[2], lo[2], nblk[2];
-  float slope[2];
+  float slope[2], slope_pos[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int row = wrow + (lane >> 2) + h * 8;
@@ -229,6 +251,7 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
     lo[h] = W > 0 ? pos[h] - W + 1 : 0;
     nblk[h] = (valid && a.pool > 0 && W > 0 && lo[h] > 0) ? lo[h] / a.pool : 0;
     slope[h] = (valid && a.slopes != nullptr) ? a.slopes[kh * G + row % G] * log2e : 0.f;
+    slope_pos[h] = -slope[h] * (float)pos[h];
   }
   const bool has_slopes = a.slopes != nullptr;
   const bool warp_live = wrow < rows_valid;
@@ -263,8 +286,13 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
       const int mat = lane >> 3;
       const unsigned char* qp = q_s + (wrow + (mat & 1) * 8 + (lane & 7)) * qs + (mat >> 1) * 16;
       const unsigned char* kp = kbuf + ((mat >> 1) * 8 + (lane & 7)) * qs + (mat & 1) * 16;
+      // with `ksplit` the column groups of a row group share the 16-wide steps of the key rows and add up their
+      // partial scores through shared memory; otherwise each forms all of them
+      const int ksteps = dk / 16;
+      const int kk0 = (CW > 1 && a.ksplit) ? cw * ksteps / CW : 0;
+      const int kk1 = (CW > 1 && a.ksplit) ? (cw + 1) * ksteps / CW : ksteps;
 #pragma unroll 2
-      for (int kk = 0; kk < dk / 16; ++kk) {
+      for (int kk = kk0; kk < kk1; ++kk) {
         unsigned qa[4];
         win_ldsm4(qa[0], qa[1], qa[2], qa[3], qp + kk * 32);
 #pragma unroll
@@ -275,9 +303,48 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
           win_mma(sc[t + 1], qa, b2, b3);
         }
       }
+      if (CW > 1 && a.ksplit) {
+        float* mine = exch_s + ((rw * CW + cw) * 32) * 32 + lane;
+#pragma unroll
+        for (int t = 0; t < NT_S; ++t)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) mine[(t * 4 + e) * 32] = sc[t][e];
+        // (the row group's warps take this branch together: whether a tile is live depends on the rows only; the
+        // buffer is written again after the tile's closing __syncthreads)
+        asm volatile("bar.sync %0, %1;" ::"r"(rw + 1), "r"(CW * 32) : "memory");
+#pragma unroll
+        for (int o2 = 1; o2 < CW; ++o2) {
+          const float* other = exch_s + ((rw * CW + (cw + o2) % CW) * 32) * 32 + lane;
+#pragma unroll
+          for (int t = 0; t < NT_S; ++t)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sc[t][e] += other[(t * 4 + e) * 32];
+        }
+      }
       // ---- scale, distance bias, mask: scores in units of log2 from here on ------------------
-      const bool edge = pooled || has_slopes || !warp_full || kb + WIN_N - 1 > wp_min || (W > 0 && kb < wp_max - W + 1);
-      if (edge) {
+      const bool edge = pooled || !warp_full || kb + WIN_N - 1 > wp_min || (W > 0 && kb < wp_max - W + 1);
+      if (has_slopes && !pooled) {
+        // score * scale - slope (pos - key), as two multiply-adds per score
+        const float kf = (float)(kb + (lane & 3) * 2);
+#pragma unroll
+        for (int t = 0; t < NT_S; ++t) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            sc[t][e] = fmaf(sc[t][e], a.scale_log2, fmaf(slope[h], kf + (float)(t * 8 + (e & 1)), slope_pos[h]));
+          }
+        }
+        if (edge) {
+#pragma unroll
+          for (int t = 0; t < NT_S; ++t) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int key = kb + t * 8 + (lane & 3) * 2 + (e & 1), h = e >> 1;
+              if (!(key <= pos[h] && key >= lo[h])) sc[t][e] = -INFINITY;
+            }
+          }
+        }
+      } else if (edge) {
 #pragma unroll
         for (int t = 0; t < NT_S; ++t) {
 #pragma unroll
@@ -285,12 +352,8 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
             const int key = kb + t * 8 + (lane & 3) * 2 + (e & 1), h = e >> 1;
             float s = sc[t][e] * a.scale_log2;
             bool seen;
-            if (pooled) {
-              seen = key < nblk[h];
-            } else {
-              s -= slope[h] * (float)(pos[h] - key);
-              seen = key <= pos[h] && key >= lo[h];
-            }
+            if (pooled) seen = key < nblk[h];
+            else seen = key <= pos[h] && key >= lo[h];
             sc[t][e] = seen ? s : -INFINITY;
           }
         }
@@ -328,12 +391,14 @@ __global__ void __launch_bounds__(WIN_RW * CW * 32) window_attention_kernel(cons
           l[e >> 1] += p;
         }
       }
+      if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {  // (a maximum moved)
 #pragma unroll
-      for (int j = 0; j < NT_O; ++j) {
-        o[j][0] *= alpha[0];
-        o[j][1] *= alpha[0];
-        o[j][2] *= alpha[1];
-        o[j][3] *= alpha[1];
+        for (int j = 0; j < NT_O; ++j) {
+          o[j][0] *= alpha[0];
+          o[j][1] *= alpha[0];
+          o[j][2] *= alpha[1];
+          o[j][3] *= alpha[1];
+        }
       }
       // ---- O += P V (this warp's columns) --------------------------------------------------------
       const unsigned char* vp = vbuf + ((mat & 1) * 8 + (lane & 7)) * vs + (c0 / 8 + (mat >> 1)) * 16;
@@ -438,23 +503,27 @@ __global__ void __launch_bounds__(128) window_merge_kernel(const WinArgs a) {
 #define WIN_SMEM_LIMIT (227 * 1024)
 #define WIN_MAX_SPLITS 64
 
-template <int DVW, int CW>
-static int launch_window(const WinArgs& a, int tokens, long long smem, cudaStream_t st) {
+template <int DVW, int CW, int RW>
+static int launch_window(WinArgs a, int tokens, long long smem, cudaStream_t st) {
+  if (CW > 1 && smem + win_exchange_bytes(a.dv) <= WIN_SMEM_LIMIT) {
+    a.ksplit = 1;
+    smem += win_exchange_bytes(a.dv);
+  }
   static long long attr_bytes = 0;  // (one per instantiation) the largest size the attribute was set for
   if (smem > attr_bytes) {
-    if (cudaFuncSetAttribute(window_attention_kernel<DVW, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+    if (cudaFuncSetAttribute(window_attention_kernel<DVW, CW, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return ULLM_ERR_LAUNCH;
-    cudaFuncSetAttribute(window_attention_kernel<DVW, CW>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    cudaFuncSetAttribute(window_attention_kernel<DVW, CW, RW>, cudaFuncAttributePreferredSharedMemoryCarveout,
                          cudaSharedmemCarveoutMaxShared);
     attr_bytes = smem;
   }
-  const int tpt = WIN_M / (a.num_q / a.num_kv);
+  const int tpt = RW * 16 / (a.num_q / a.num_kv);
   // at most ceil(tokens / tpt) + num_requests token tiles exist, however the tokens are spread
   const long long blocks = ((long long)(tokens + tpt - 1) / tpt + a.num_requests) * a.num_kv;
   if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
-  const int rc = ullm_launch_kernel(window_attention_kernel<DVW, CW>, dim3((unsigned)blocks, (unsigned)a.nsplit),
-                                    dim3(WIN_RW * CW * 32), (size_t)smem, st, a);
+  const int rc = ullm_launch_kernel(window_attention_kernel<DVW, CW, RW>, dim3((unsigned)blocks, (unsigned)a.nsplit),
+                                    dim3(RW * CW * 32), (size_t)smem, st, a);
   if (rc != ULLM_OK || a.nsplit <= 1) return rc;
   return ullm_launch_kernel(window_merge_kernel, dim3((unsigned)((long long)tokens * a.num_q)), dim3(128), 0, st, a);
 }
@@ -463,7 +532,7 @@ static int launch_window(const WinArgs& a, int tokens, long long smem, cudaStrea
 // heads per kv head, and tiles that fit the shared memory (key rows up to 576 with values inside them).
 extern "C" int ullm_window_attention_supported(int dk, int dv, int num_q, int num_kv, int values_in_keys) {
   if (dk <= 0 || dv <= 0 || num_q <= 0 || num_kv <= 0 || num_q % num_kv) return 0;
-  if (dk % 16 || dv % 16 || dv > 512 || num_q / num_kv > WIN_M) return 0;
+  if (dk % 16 || dv % 16 || dv > 512 || num_q / num_kv > WIN_MAX_GROUP) return 0;
   if (values_in_keys && dv > dk) return 0;
   return win_smem_bytes(dk, dv, !values_in_keys) <= WIN_SMEM_LIMIT;
 }
@@ -530,9 +599,9 @@ extern "C" int ullm_window_attention(const void* q, long long q_row_stride, void
   a.nsplit = nsplit;
   a.parts = parts;
   const long long smem = win_smem_bytes(dk, dv, v_cache != nullptr);
-  if (dv <= 64) return launch_window<64, 1>(a, tokens, smem, st);
-  if (dv <= 128) return launch_window<128, 1>(a, tokens, smem, st);
-  if (dv <= 256) return launch_window<128, 2>(a, tokens, smem, st);
-  if (dv <= 384) return launch_window<192, 2>(a, tokens, smem, st);
-  return launch_window<256, 2>(a, tokens, smem, st);
+  if (dv <= 64) return launch_window<64, 1, 4>(a, tokens, smem, st);
+  if (dv <= 128) return launch_window<128, 1, 4>(a, tokens, smem, st);
+  if (dv <= 256) return launch_window<128, 2, 4>(a, tokens, smem, st);
+  if (dv <= 384) return launch_window<192, 2, 4>(a, tokens, smem, st);
+  return launch_window<256, 2, 4>(a, tokens, smem, st);
 }
