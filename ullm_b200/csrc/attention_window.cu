@@ -101,7 +101,7 @@ static inline int win_row_groups(int dv) { return 4; }
 static inline int win_col_groups(int dv) { return dv <= 128 ? 1 : 2; }
 static inline long long win_smem_bytes(int dk, int dv, bool v_own) {
   const long long qs = dk * 2 + 16, vs = dv * 2 + 16;
-  return 16LL * win_row_groups(dv) * qs + 2LL * WIN_N * qs + (v_own ? 2LL * WIN_N * vs : 0) + 2LL * WIN_N * 8;
+  return 16LL * win_row_groups(dv) * qs + 2LL * WIN_N * qs + (v_own ? 1LL * WIN_N * vs : 0) + 2LL * WIN_N * 8;
 }
 // the partial scores that the column groups of a row group exchange: [row group][column group][32 registers][lane]
 static inline long long win_exchange_bytes(int dv) {
@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(RW * CW * 32) window_attention_kernel(const Wi
   unsigned char* q_s = smem;
   unsigned char* k_s = q_s + WIN_M * qs;
   unsigned char* v_s = k_s + 2 * WIN_N * qs;
-  long long* slot_s = reinterpret_cast<long long*>(v_s + (v_own ? 2 * WIN_N * vs : 0));
+  long long* slot_s = reinterpret_cast<long long*>(v_s + (v_own ? WIN_N * vs : 0));
   float* exch_s = reinterpret_cast<float*>(slot_s + 2 * WIN_N);  // only with `ksplit`
 
   // consecutive blocks are the same token tile of all kv heads, the last tiles (most keys) first
@@ -192,10 +192,27 @@ __global__ void __launch_bounds__(RW * CW * 32) window_attention_kernel(const Wi
 
   const int k_row0 = tid / kchunks, k_ch0 = tid % kchunks, k_drow = THREADS / kchunks, k_dch = THREADS % kchunks;
   const int v_row0 = tid / vchunks, v_ch0 = tid % vchunks, v_drow = THREADS / vchunks, v_dch = THREADS % vchunks;
+  // Keys have two stages, value pages of their own ONE (with two, a block of 128-wide heads takes 87 KB and two
+  // fit an SM; with one, three): tile t's values are asked for when tile t - 1's are used up, and awaited
+  // between the softmax and P V of tile t.
+  auto issue_values = [&](int tile) {
+    const long long* slots = slot_s + (tile & 1) * WIN_N;
+    const __nv_bfloat16* vc = (tile < ptiles ? a.pv : a.v_cache) + (long long)kh * dv;
+    for (int row = v_row0, ch = v_ch0; row < WIN_N;) {
+      const long long s = slots[row];
+      const bool ok = s >= 0;
+      win_cp_async_16(v_s + row * vs + ch * 16, vc + (ok ? s * v_row + ch * 8 : 0), ok);
+      row += v_drow;
+      ch += v_dch;
+      if (ch >= vchunks) {
+        ch -= vchunks;
+        ++row;
+      }
+    }
+  };
   auto issue = [&](int tile) {
     const int st = tile & 1;
     unsigned char* kbuf = k_s + st * WIN_N * qs;
-    unsigned char* vbuf = v_s + st * WIN_N * vs;
     long long* slots = slot_s + st * WIN_N;
     const bool pooled = tile < ptiles;
     if (tid < WIN_N) {
@@ -220,20 +237,6 @@ __global__ void __launch_bounds__(RW * CW * 32) window_attention_kernel(const Wi
       if (ch >= kchunks) {
         ch -= kchunks;
         ++row;
-      }
-    }
-    if (v_own) {
-      const __nv_bfloat16* vc = (pooled ? a.pv : a.v_cache) + (long long)kh * dv;
-      for (int row = v_row0, ch = v_ch0; row < WIN_N;) {
-        const long long s = slots[row];
-        const bool ok = s >= 0;
-        win_cp_async_16(vbuf + row * vs + ch * 16, vc + (ok ? s * v_row + ch * 8 : 0), ok);
-        row += v_drow;
-        ch += v_dch;
-        if (ch >= vchunks) {
-          ch -= vchunks;
-          ++row;
-        }
       }
     }
   };
@@ -268,19 +271,28 @@ __global__ void __launch_bounds__(RW * CW * 32) window_attention_kernel(const Wi
 #pragma unroll
   for (int j = 0; j < NT_O; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
 
-  if (t_begin < t_end) issue(t_begin);
+  // cp.async groups, oldest first: [Q] K(b) V(b) | K(b+1) | V(b+1) K(b+2) | ...  (the V groups only with value
+  // pages of their own): at the top of tile t the two newest groups (V(t), K(t+1)) may be in flight, in front
+  // of P V only K(t+1)
+  if (t_begin < t_end) issue(t_begin);  // (its __syncthreads publishes the slots that issue_values reads)
   win_commit();
+  if (v_own) {
+    if (t_begin < t_end) issue_values(t_begin);
+    win_commit();
+  }
   for (int it = t_begin; it < t_end; ++it) {
     if (it + 1 < t_end) issue(it + 1);
     win_commit();
-    win_wait<1>();
+    if (v_own) win_wait<2>();
+    else win_wait<1>();
     __syncthreads();
     const bool pooled = it < ptiles;
     const int kb = pooled ? it * WIN_N : key0 + (it - ptiles) * WIN_N;
-    if (warp_live && (pooled ? kb < w_nblk : (kb <= wp_max && kb + WIN_N - 1 >= wp_lo))) {
-      const unsigned char* kbuf = k_s + (it & 1) * WIN_N * qs;
-      const unsigned char* vbuf = v_own ? v_s + (it & 1) * WIN_N * vs : kbuf;
-      float sc[NT_S][4];
+    const bool live = warp_live && (pooled ? kb < w_nblk : (kb <= wp_max && kb + WIN_N - 1 >= wp_lo));
+    const unsigned char* kbuf = k_s + (it & 1) * WIN_N * qs;
+    const unsigned char* vbuf = v_own ? v_s : kbuf;
+    float sc[NT_S][4];
+    if (live) {
 #pragma unroll
       for (int t = 0; t < NT_S; ++t) sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.f;
       const int mat = lane >> 3;
@@ -400,6 +412,13 @@ __global__ void __launch_bounds__(RW * CW * 32) window_attention_kernel(const Wi
           o[j][3] *= alpha[1];
         }
       }
+    }
+    if (v_own) {
+      win_wait<1>();
+      __syncthreads();
+    }
+    if (live) {
+      const int mat = lane >> 3;
       // ---- O += P V (this warp's columns) --------------------------------------------------------
       const unsigned char* vp = vbuf + ((mat & 1) * 8 + (lane & 7)) * vs + (c0 / 8 + (mat >> 1)) * 16;
 #pragma unroll
@@ -421,6 +440,10 @@ __global__ void __launch_bounds__(RW * CW * 32) window_attention_kernel(const Wi
       }
     }
     __syncthreads();
+    if (v_own) {
+      if (it + 1 < t_end) issue_values(it + 1);
+      win_commit();
+    }
   }
   win_wait<0>();
   const int c = (lane & 3) * 2;
