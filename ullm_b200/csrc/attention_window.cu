@@ -95,10 +95,10 @@ __device__ __forceinline__ unsigned win_pack(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-// values up to 128 wide: one column group; wider: two.  Four row groups (with eight, 256 threads of about 170
+// values up to 128 wide: one column group; up to 256: two; up to 384: three of 128; up to 512: two of 256.  Four row groups (with eight, 256 threads of about 170
 // registers leave one block per SM; four leave three)
 static inline int win_row_groups(int dv) { return 4; }
-static inline int win_col_groups(int dv) { return dv <= 128 ? 1 : 2; }
+static inline int win_col_groups(int dv) { return dv <= 128 ? 1 : (dv > 256 && dv <= 384 ? 3 : 2); }
 static inline long long win_smem_bytes(int dk, int dv, bool v_own) {
   const long long qs = dk * 2 + 16, vs = dv * 2 + 16;
   return 16LL * win_row_groups(dv) * qs + 2LL * WIN_N * qs + (v_own ? 1LL * WIN_N * vs : 0) + 2LL * WIN_N * 8;
@@ -625,6 +625,6 @@ extern "C" int ullm_window_attention(const void* q, long long q_row_stride, void
   if (dv <= 64) return launch_window<64, 1, 4>(a, tokens, smem, st);
   if (dv <= 128) return launch_window<128, 1, 4>(a, tokens, smem, st);
   if (dv <= 256) return launch_window<128, 2, 4>(a, tokens, smem, st);
-  if (dv <= 384) return launch_window<192, 2, 4>(a, tokens, smem, st);
+  if (dv <= 384) return launch_window<128, 3, 4>(a, tokens, smem, st);
   return launch_window<256, 2, 4>(a, tokens, smem, st);
 }
