@@ -237,7 +237,8 @@ def one_key_model(kind, size, pool, dtype, dim):
         grow = ["l0.mix.left.q.norm"]
     else:
         # (scores grow with the rank: the scale keeps the sharpness of the small ranks)
-        m = latent(2, dim, 16, 24, dim, 24, min(1.0, 48.0 / dim), size, base=50.0)
+        rot = 64 if dim in (384, 512) else 16  # (key rows of 384 + 64 and 512 + 64: sizes the kernel knows as constants)
+        m = latent(2, dim, rot, 24, dim, 24, min(1.0, 48.0 / dim), size, base=50.0)
         grow = ["l0.mix.uq"]
     cfg = config(48, 61, [(kind, m, None)], scale=3.0)
     w = pp.random_weights(cfg, seed=size * 31 + pool)
@@ -257,7 +258,8 @@ def with_mask(cfg, size, pool):
 EDGES = [("attention", 8, 4, 32), ("attention", 4, 4, 64), ("attention", 70, 2, 64), ("attention", 5, 3, 128), ("attention", 17, 1, 24),
          ("attention", 9, 0, 64), ("parallel", 8, 0, 32), ("parallel", 17, 0, 64), ("latent_attention", 8, 0, 32),
          ("latent_attention", 19, 0, 48), ("parallel", 66, 0, 128), ("latent_attention", 67, 0, 160),
-         ("latent_attention", 65, 0, 272), ("latent_attention", 21, 0, 400)]
+         ("latent_attention", 65, 0, 272), ("latent_attention", 21, 0, 400),
+         ("latent_attention", 66, 0, 384), ("latent_attention", 33, 0, 512)]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

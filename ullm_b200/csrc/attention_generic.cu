@@ -23,6 +23,7 @@
 #include "common.cuh"
 
 #define ATT_MAX_HEAD_DIM 512
+#define ATT_MAX_KEY_DIM 640  // key rows that carry more than a head's values (a latent and a rotated part)
 #define ATT_WARPS 4
 #define ATT_O_REGS (ATT_MAX_HEAD_DIM / 32)
 
@@ -63,7 +64,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, long lon
                                                int head_dim, int page_size, int window, float scale,
                                                long long num_pages, int* status, int v_dim, int keep_first,
                                                float softcap, int v_rep, float* __restrict__ out_f32, AttExtras ex) {
-  __shared__ float qs[ATT_WARPS][ATT_MAX_HEAD_DIM];
+  __shared__ float qs[ATT_WARPS][ATT_MAX_KEY_DIM];
   pdl_launch_dependents();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -321,7 +322,7 @@ extern "C" int ullm_paged_attention_generic_ex3(int dtype, const void* q, long l
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens < 0 || num_q <= 0 || num_kv <= 0 || head_dim <= 0 || page_size <= 0 || max_pages <= 0)
     return ULLM_ERR_BAD_SIZE;
-  if (num_q % num_kv != 0 || head_dim > ATT_MAX_HEAD_DIM || window < 0 || v_dim <= 0 || v_dim > ATT_MAX_HEAD_DIM ||
+  if (num_q % num_kv != 0 || head_dim > ATT_MAX_KEY_DIM || window < 0 || v_dim <= 0 || v_dim > ATT_MAX_HEAD_DIM ||
       keep_first < 0 || softcap < 0.f || pool < 0)
     return ULLM_ERR_UNSUPPORTED;
   if (values_in_keys && v_dim > head_dim) return ULLM_ERR_BAD_SIZE;

@@ -63,6 +63,8 @@ __global__ void kv_shared_prepare_kernel(T* __restrict__ qk, long long stride, i
   }
 }
 
+#define POOL_SLOTS 1024
+
 // One block per token; a token whose pooled slot is -1 completes no block.  The block's positions are
 // pos - pool + 1 .. pos of the token's request, found through the request's row of the block table.
 template <typename T>
@@ -86,6 +88,34 @@ __global__ void pool_blocks_kernel(const int* __restrict__ positions, const int*
   const int* bt = block_table + (long long)req_slots[r] * max_pages;
   const float inv = 1.f / (float)pool;
   const int cols = row + (v_pages != nullptr ? v_row : 0);
+  // blocks of up to POOL_SLOTS positions: their slots are found once; the sums then run over them without a
+  // branch, eight loads in flight, in the order of the positions
+  __shared__ long long slot_s[POOL_SLOTS];
+  if (pool <= POOL_SLOTS) {
+    int bad = 0;
+    for (int i = threadIdx.x; i < pool; i += blockDim.x) {
+      const int j = pos - pool + 1 + i;
+      const int page = j >= 0 ? bt[j / page_size] : -1;
+      if (page < 0 || page >= num_pages) {
+        bad = 1;
+        ullm_report(status, ULLM_STATUS_PAGE, t, page);
+      } else {
+        slot_s[i] = (long long)page * page_size + j % page_size;
+      }
+    }
+    if (__syncthreads_or(bad)) return;  // (nothing is written for a block whose pages are not there)
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+      const bool is_v = c >= row;
+      const T* src = is_v ? v_pages + (c - row) : k_pages + c;
+      const long long stride = is_v ? v_row : row;
+      float acc = 0.f;
+#pragma unroll 8
+      for (int i = 0; i < pool; ++i) acc += to_f32(src[slot_s[i] * stride]);
+      if (is_v) pv_pages[dst * v_row + (c - row)] = from_f32<T>(acc * inv);
+      else pk_pages[dst * row + c] = from_f32<T>(acc * inv);
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < cols; c += blockDim.x) {
     const bool is_v = c >= row;
     float acc = 0.f;

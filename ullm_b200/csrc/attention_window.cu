@@ -108,7 +108,9 @@ static inline long long win_exchange_bytes(int dv) {
   return win_col_groups(dv) > 1 ? 4096LL * win_row_groups(dv) * win_col_groups(dv) : 0;
 }
 
-template <int DVW, int CW, int RW>
+// DKT > 0: the key rows are DKT wide and the values DVW x CW, known to the compiler (strides, piece counts and the
+// steps of Q K^T become constants and the loops unroll); DKT = 0: both are read from the arguments.
+template <int DVW, int CW, int RW, int DKT>
 __global__ void __launch_bounds__(RW * CW * 32) window_attention_kernel(const WinArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_launch_dependents();
@@ -116,7 +118,7 @@ __global__ void __launch_bounds__(RW * CW * 32) window_attention_kernel(const Wi
   constexpr int NT_S = WIN_N / 8, NT_O = DVW / 8, THREADS = RW * CW * 32, WIN_M = RW * 16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rw = warp % RW, cw = warp / RW;
-  const int dk = a.dk, dv = a.dv, W = a.window, page_size = a.page_size;
+  const int dk = DKT > 0 ? DKT : a.dk, dv = DKT > 0 ? DVW * CW : a.dv, W = a.window, page_size = a.page_size;
   const bool v_own = a.v_cache != nullptr;
   const int qs = dk * 2 + 16;               // bytes between rows of the Q and K tiles
   const int vs = v_own ? dv * 2 + 16 : qs;  // ... of the tile the values are read from
@@ -303,7 +305,7 @@ __global__ void __launch_bounds__(RW * CW * 32) window_attention_kernel(const Wi
       const int ksteps = dk / 16;
       const int kk0 = (CW > 1 && a.ksplit) ? cw * ksteps / CW : 0;
       const int kk1 = (CW > 1 && a.ksplit) ? (cw + 1) * ksteps / CW : ksteps;
-#pragma unroll 2
+#pragma unroll(DKT > 0 ? (DKT / 16 <= 8 ? DKT / 16 : 4) : 2)
       for (int kk = kk0; kk < kk1; ++kk) {
         unsigned qa[4];
         win_ldsm4(qa[0], qa[1], qa[2], qa[3], qp + kk * 32);
@@ -526,7 +528,7 @@ __global__ void __launch_bounds__(128) window_merge_kernel(const WinArgs a) {
 #define WIN_SMEM_LIMIT (227 * 1024)
 #define WIN_MAX_SPLITS 64
 
-template <int DVW, int CW, int RW>
+template <int DVW, int CW, int RW, int DKT = 0>
 static int launch_window(WinArgs a, int tokens, long long smem, cudaStream_t st) {
   if (CW > 1 && smem + win_exchange_bytes(a.dv) <= WIN_SMEM_LIMIT) {
     a.ksplit = 1;
@@ -534,10 +536,10 @@ static int launch_window(WinArgs a, int tokens, long long smem, cudaStream_t st)
   }
   static long long attr_bytes = 0;  // (one per instantiation) the largest size the attribute was set for
   if (smem > attr_bytes) {
-    if (cudaFuncSetAttribute(window_attention_kernel<DVW, CW, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+    if (cudaFuncSetAttribute(window_attention_kernel<DVW, CW, RW, DKT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return ULLM_ERR_LAUNCH;
-    cudaFuncSetAttribute(window_attention_kernel<DVW, CW, RW>, cudaFuncAttributePreferredSharedMemoryCarveout,
+    cudaFuncSetAttribute(window_attention_kernel<DVW, CW, RW, DKT>, cudaFuncAttributePreferredSharedMemoryCarveout,
                          cudaSharedmemCarveoutMaxShared);
     attr_bytes = smem;
   }
@@ -545,7 +547,7 @@ static int launch_window(WinArgs a, int tokens, long long smem, cudaStream_t st)
   // at most ceil(tokens / tpt) + num_requests token tiles exist, however the tokens are spread
   const long long blocks = ((long long)(tokens + tpt - 1) / tpt + a.num_requests) * a.num_kv;
   if (blocks > 0x7fffffffLL) return ULLM_ERR_BAD_SIZE;
-  const int rc = ullm_launch_kernel(window_attention_kernel<DVW, CW, RW>, dim3((unsigned)blocks, (unsigned)a.nsplit),
+  const int rc = ullm_launch_kernel(window_attention_kernel<DVW, CW, RW, DKT>, dim3((unsigned)blocks, (unsigned)a.nsplit),
                                     dim3(RW * CW * 32), (size_t)smem, st, a);
   if (rc != ULLM_OK || a.nsplit <= 1) return rc;
   return ullm_launch_kernel(window_merge_kernel, dim3((unsigned)((long long)tokens * a.num_q)), dim3(128), 0, st, a);
@@ -622,6 +624,11 @@ extern "C" int ullm_window_attention(const void* q, long long q_row_stride, void
   a.nsplit = nsplit;
   a.parts = parts;
   const long long smem = win_smem_bytes(dk, dv, v_cache != nullptr);
+  // the sizes of the usual head shapes (64, 128; latents of 384 + 64 and 512 + 64) as constants
+  if (dk == 64 && dv == 64) return launch_window<64, 1, 4, 64>(a, tokens, smem, st);
+  if (dk == 128 && dv == 128) return launch_window<128, 1, 4, 128>(a, tokens, smem, st);
+  if (dk == 448 && dv == 384) return launch_window<128, 3, 4, 448>(a, tokens, smem, st);
+  if (dk == 576 && dv == 512) return launch_window<256, 2, 4, 576>(a, tokens, smem, st);
   if (dv <= 64) return launch_window<64, 1, 4>(a, tokens, smem, st);
   if (dv <= 128) return launch_window<128, 1, 4>(a, tokens, smem, st);
   if (dv <= 256) return launch_window<128, 2, 4>(a, tokens, smem, st);

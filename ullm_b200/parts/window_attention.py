@@ -182,8 +182,9 @@ class LatentAttention(Mixer):
         super().__init__()
         if min(hidden_size, num_heads, head_dim, value_dim, q_rank, kv_rank) <= 0 or rot_dim < 0:
             raise ValueError("sizes must be positive")
-        if kv_rank + rot_dim > 512:
-            raise ValueError(f"kv_rank + rot_dim = {kv_rank + rot_dim}: the attention kernel takes rows up to 512")
+        if kv_rank + rot_dim > 640 or kv_rank > 512:
+            raise ValueError(f"kv_rank {kv_rank} + rot_dim {rot_dim}: the attention kernels take key rows up to 640 "
+                             "and values up to 512")
         if window is not None and window <= 0:
             raise ValueError("window must be positive (None: every earlier token is seen)")
         if pool < 0 or (pool and window is None):
