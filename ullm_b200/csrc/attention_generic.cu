@@ -1,6 +1,7 @@
 // Paged causal attention for any mix of requests in one flat batch: prompt
 // portions of any length beside single decoded tokens.  This is the general
-// kernel: any head size up to 512, any head counts, any page size, optional
+// kernel: any head size up to 512 (key rows up to 640 where the values are a
+// narrower part of them), any head counts, any page size, optional
 // sliding window, float32 or bfloat16 storage.  It is the whole attention of
 // the 32-bit path and the fallback of the bfloat16 path for sizes its
 // tensor-core kernels do not take.
