@@ -111,7 +111,7 @@ static inline long long win_exchange_bytes(int dv) {
 // DKT > 0: the key rows are DKT wide and the values DVW x CW, known to the compiler (strides, piece counts and the
 // steps of Q K^T become constants and the loops unroll); DKT = 0: both are read from the arguments.
 template <int DVW, int CW, int RW, int DKT>
-__global__ void __launch_bounds__(RW * CW * 32) window_attention_kernel(const WinArgs a) {
+__global__ void __launch_bounds__(RW * CW * 32, CW == 1 ? 3 : 1) window_attention_kernel(const WinArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_launch_dependents();
   pdl_wait();
