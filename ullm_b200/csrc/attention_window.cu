@@ -2,21 +2,23 @@
 // decoded tokens, with the options of the general kernel's `AttExtras` (csrc/attention_generic.cu): values that
 // are the first `dv` elements of the key rows, distance slopes, pooled blocks behind the window, an output gate,
 // an output scale and a row stride of the output.  Key rows of any size that is a multiple of 16 (the QK loop
-// runs over a runtime count of 16-wide steps), values up to 512 wide.
+// runs over a runtime count of 16-wide steps; the usual sizes are also compiled as constants), values up to 512.
 //
 // Flash-attention style, mma.sync m16n8k16 bf16 with 32-bit accumulation; scores, maxima, sums, the distance
 // bias and the output accumulator are 32-bit.  A block owns 64 rows of one kv head for one request; rows are
 // (token, query head of the group) pairs, so with G query heads per kv head it covers 64 / G tokens and one pass
 // over the keys serves all heads that share them (latent attention: one kv head, G = all heads).  The block's
-// warps form a grid of 4 row groups (16 rows each) x CW column groups: every warp of a row group forms the same
-// scores and weights and applies them to its own DVW of the value columns, so the output accumulator of wide
-// values is spread over CW warps' registers.
+// warps form a grid of 4 row groups (16 rows each) x CW column groups: the warps of a row group split the
+// 16-wide steps of Q K^T, add their partial scores through shared memory, form the same weights and apply them to
+// their own DVW of the value columns, so the output accumulator of wide values is spread over CW warps' registers.
 //
 // Key tiles of 64, gathered from the pages by cp.async into a two-stage ring (rows padded by 16 bytes: with a
-// row size that is a multiple of 32 bytes the eight rows of an ldmatrix fall into distinct banks).  A block
-// walks first the pooled entries its rows can see (entry b stands for positions bP .. bP + P - 1 and is seen by
-// a row at position i when bP + P - 1 <= i - window), then the keys from the window's start of its first token
-// to its last token.  All stretches share one online softmax.
+// row size that is a multiple of 32 bytes the eight rows of an ldmatrix fall into distinct banks); value pages
+// of their own have one stage, awaited between the softmax and P V.  A block walks first the pooled entries its
+// rows can see (entry b stands for positions bP .. bP + P - 1 and is seen by a row at position i when
+// bP + P - 1 <= i - window), then the keys from the window's start of its first token to its last token.  All
+// stretches share one online softmax.  For steps of few rows the tiles of a block are cut into runs (grid.y)
+// whose unnormalised results a second kernel merges.  The only waits are cp.async groups and block barriers.
 #include "common.cuh"
 
 #define WIN_N 64
