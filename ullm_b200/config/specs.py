@@ -75,12 +75,15 @@ class ScheduleEntry:
     entry whose cache this execution reads instead of writing one of its own.
     What is added to the residual stream right before this execution (a pass of a loop over layers starts here,
     say): `add_input` the model's input as the embedding left it, `add_vector` row of the model's table of pass
-    vectors (`ModelSpec.pass_vectors`); input first, then the vector."""
+    vectors (`ModelSpec.pass_vectors`); input first, then the vector.  `project_input`: right before this execution
+    the stream is REPLACED by a projection of [stream | the model's input as the embedding left it] with the
+    model's pass projection (`ModelSpec.pass_projection`, [hidden, 2 hidden]); before any addition."""
 
     layer: int
     cache_of: int | None = None
     add_input: bool = False
     add_vector: int | None = None
+    project_input: bool = False
 
 
 @dataclass(frozen=True)
@@ -125,6 +128,9 @@ class ModelSpec:
     # (tensor name, rows): a table [rows, hidden] of vectors that schedule entries add to the stream
     # (`ScheduleEntry.add_vector`); needs stream_dtype="float32"
     pass_vectors: tuple[str, int] | None = None
+    # tensor name of a matrix [hidden, 2 hidden] that maps [stream | embedding output] to the new stream before the
+    # schedule entries that say `project_input`; needs stream_dtype="float32"
+    pass_projection: str | None = None
 
     def validate(self) -> None:
         if not self.layers:
@@ -136,7 +142,9 @@ class ModelSpec:
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.layers)}")
             if e.add_vector is not None and (self.pass_vectors is None or not 0 <= e.add_vector < self.pass_vectors[1]):
                 raise ValueError(f"schedule entry {i}: add_vector={e.add_vector} names no row of the pass vectors")
-            if (e.add_input or e.add_vector is not None) and self.stream_dtype != "float32":
+            if e.project_input and self.pass_projection is None:
+                raise ValueError(f"schedule entry {i}: project_input without a pass projection")
+            if (e.add_input or e.add_vector is not None or e.project_input) and self.stream_dtype != "float32":
                 raise ValueError(f"schedule entry {i}: additions to the stream need stream_dtype='float32'")
             if e.cache_of is not None:
                 if not 0 <= e.cache_of < i:

@@ -12,8 +12,15 @@
 //                       kv head (the values are its first `rank` elements); a query row per head is
 //                       [q_h W_uk,h (from a batched product) | rotated q_rot,h]
 //
-// Rotation: neighbours (2i, 2i + 1), i < dims / 2, turn by the 32-bit angle position * f_i (f_i from a table built
-// in 64-bit); sincosf is the accurate form.  Sums and norms are 32-bit; one rounding at each store.
+//   qkv_rows_prepare    grouped attention with q | k | v projections: an optional RMS norm of q and of k over the
+//                       WHOLE projection (a weight per channel), then the rotation of the first `rot_dims`
+//                       dimensions of every q and k head, a factor per query head on q, and every value head
+//                       divided by its root mean square (no weight); q goes to a buffer of its own, k and v to
+//                       their pages
+//
+// Rotation: with `interleaved` neighbours (2i, 2i + 1), otherwise (i, i + dims / 2), i < dims / 2, turn by the
+// 32-bit angle position * f_i (f_i from a table built in 64-bit); sincosf is the accurate form.  Sums and norms
+// are 32-bit; one rounding at each store.
 #include "common.cuh"
 
 // One block per token.  qk: [tokens][stride], q in columns 0 .. q_size-1, k in q_size .. q_size + kv_size - 1.
@@ -141,8 +148,8 @@ __global__ void pool_blocks_kernel(const int* __restrict__ positions, const int*
 template <typename T>
 __global__ void latent_prepare_kernel(const T* __restrict__ q_full, const T* __restrict__ q_lat,
                                       const T* __restrict__ dkv, T* __restrict__ q_out, int tokens, int heads,
-                                      int dim, int rot, int rank, int rot_dims, const float* __restrict__ w_c,
-                                      float eps, const float* __restrict__ inv_freq,
+                                      int dim, int rot, int rank, int rot_dims, int interleaved,
+                                      const float* __restrict__ w_c, float eps, const float* __restrict__ inv_freq,
                                       const int* __restrict__ positions, const int* __restrict__ slot_mapping,
                                       T* __restrict__ k_pages, long long num_slots, int* status) {
   __shared__ float scratch[33];
@@ -151,6 +158,7 @@ __global__ void latent_prepare_kernel(const T* __restrict__ q_full, const T* __r
   const int t = blockIdx.x;
   const float p = (float)positions[t];
   const int kw = rank + rot;
+  const int half = rot_dims >> 1;
   // queries: the absorbed part is copied, the rotated part turned
   for (int i = threadIdx.x; i < heads * rank; i += blockDim.x) {
     const int h = i / rank, c = i - h * rank;
@@ -161,10 +169,12 @@ __global__ void latent_prepare_kernel(const T* __restrict__ q_full, const T* __r
     const T* src = q_full + ((long long)t * heads + h) * (dim + rot) + dim;
     float v = to_f32(src[c]);
     if (c < rot_dims) {
+      const bool second = interleaved ? (c & 1) : (c >= half);
+      const int pc = interleaved ? (c ^ 1) : (second ? c - half : c + half);
       float sn, cs;
-      sincosf(p * inv_freq[c >> 1], &sn, &cs);
-      const float other = to_f32(src[c ^ 1]);
-      v = (c & 1) ? v * cs + other * sn : v * cs - other * sn;
+      sincosf(p * inv_freq[interleaved ? (c >> 1) : (second ? c - half : c)], &sn, &cs);
+      const float other = to_f32(src[pc]);
+      v = second ? v * cs + other * sn : v * cs - other * sn;
     }
     q_out[((long long)t * heads + h) * kw + rank + c] = from_f32<T>(v);
   }
@@ -187,12 +197,104 @@ __global__ void latent_prepare_kernel(const T* __restrict__ q_full, const T* __r
   for (int c = threadIdx.x; c < rot; c += blockDim.x) {
     float v = to_f32(row[rank + c]);
     if (c < rot_dims) {
+      const bool second = interleaved ? (c & 1) : (c >= half);
+      const int pc = interleaved ? (c ^ 1) : (second ? c - half : c + half);
       float sn, cs;
-      sincosf(p * inv_freq[c >> 1], &sn, &cs);
-      const float other = to_f32(row[rank + (c ^ 1)]);
-      v = (c & 1) ? v * cs + other * sn : v * cs - other * sn;
+      sincosf(p * inv_freq[interleaved ? (c >> 1) : (second ? c - half : c)], &sn, &cs);
+      const float other = to_f32(row[rank + pc]);
+      v = second ? v * cs + other * sn : v * cs - other * sn;
     }
     dst[rank + c] = from_f32<T>(v);
+  }
+}
+
+#define ROWS_MAX_ROT 512
+
+// One block per token.  qkv [tokens][stride]: q (num_q heads of head_dim) | k (num_kv heads of head_dim) | v (num_kv
+// heads of v_dim) as projected; q_out [tokens][num_q * head_dim].
+template <typename T>
+__global__ void qkv_rows_prepare_kernel(const T* __restrict__ qkv, long long stride, T* __restrict__ q_out, int num_q,
+                                        int num_kv, int head_dim, int v_dim, const float* __restrict__ wq,
+                                        const float* __restrict__ wk, float eps, const float* __restrict__ inv_freq,
+                                        int rot_dims, int interleaved, const int* __restrict__ positions,
+                                        const float* __restrict__ q_head_scale, int v_unit,
+                                        const int* __restrict__ slot_mapping, T* __restrict__ k_pages,
+                                        T* __restrict__ v_pages, long long num_slots, int* status) {
+  __shared__ float scratch[33];
+  __shared__ float cs_s[ROWS_MAX_ROT / 2], sn_s[ROWS_MAX_ROT / 2];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int q_size = num_q * head_dim, k_size = num_kv * head_dim, v_size = num_kv * v_dim;
+  const T* q = qkv + (long long)t * stride;
+  const T* k = q + q_size;
+  const T* v = k + k_size;
+  long long slot = slot_mapping != nullptr ? slot_mapping[t] : -1;
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) ullm_report(status, ULLM_STATUS_SLOT, t, (int)slot);
+    slot = -1;
+  }
+  const int half = rot_dims >> 1;
+  if (rot_dims > 0) {
+    const float p = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(p * inv_freq[i], &sn_s[i], &cs_s[i]);
+  }
+  float rq = 1.f, rk = 1.f;
+  if (wq != nullptr) {
+    float acc = 0.f;
+    for (int c = threadIdx.x; c < q_size; c += blockDim.x) {
+      const float x = to_f32(q[c]);
+      acc += x * x;
+    }
+    rq = 1.f / sqrtf(block_sum(acc, scratch) / (float)q_size + eps);
+    acc = 0.f;
+    for (int c = threadIdx.x; c < k_size; c += blockDim.x) {
+      const float x = to_f32(k[c]);
+      acc += x * x;
+    }
+    rk = 1.f / sqrtf(block_sum(acc, scratch) / (float)k_size + eps);
+  } else {
+    __syncthreads();  // (the angles)
+  }
+  // q and k: norm, rotation, (q) the head's factor
+  for (int c = threadIdx.x; c < q_size + k_size; c += blockDim.x) {
+    const bool is_q = c < q_size;
+    const int cc = is_q ? c : c - q_size;
+    const T* src = is_q ? q : k;
+    const float* w = is_q ? wq : wk;
+    const float r = is_q ? rq : rk;
+    const int h = cc / head_dim, j = cc - h * head_dim;
+    float x = to_f32(src[cc]) * r * (w != nullptr ? w[cc] : 1.f);
+    if (j < rot_dims) {
+      const bool second = interleaved ? (j & 1) : (j >= half);
+      const int pj = interleaved ? (j ^ 1) : (second ? j - half : j + half);
+      const int fi = interleaved ? (j >> 1) : (second ? j - half : j);
+      const int pc = h * head_dim + pj;
+      const float other = to_f32(src[pc]) * r * (w != nullptr ? w[pc] : 1.f);
+      x = second ? x * cs_s[fi] + other * sn_s[fi] : x * cs_s[fi] - other * sn_s[fi];
+    }
+    if (is_q) {
+      if (q_head_scale != nullptr) x *= q_head_scale[h];
+      q_out[(long long)t * q_size + cc] = from_f32<T>(x);
+    } else if (slot >= 0) {
+      k_pages[slot * k_size + cc] = from_f32<T>(x);
+    }
+  }
+  if (slot < 0) return;
+  // v: a warp per value head
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int g = warp; g < num_kv; g += warps) {
+    const T* src = v + g * v_dim;
+    float r = 1.f;
+    if (v_unit) {
+      float acc = 0.f;
+      for (int j = lane; j < v_dim; j += 32) {
+        const float x = to_f32(src[j]);
+        acc += x * x;
+      }
+      r = 1.f / sqrtf(warp_sum(acc) / (float)v_dim + eps);
+    }
+    for (int j = lane; j < v_dim; j += 32) v_pages[slot * v_size + g * v_dim + j] = from_f32<T>(to_f32(src[j]) * r);
   }
 }
 
@@ -246,7 +348,7 @@ extern "C" int ullm_pool_blocks(int dtype, const int* positions, const int* toke
 extern "C" int ullm_latent_prepare(int dtype, const void* q_full, const void* q_lat, const void* dkv, void* q_out,
                                    int tokens, int heads, int dim, int rot, int rank, int rot_dims, const float* w_c,
                                    float eps, const float* inv_freq, const int* positions, const int* slot_mapping,
-                                   void* k_pages, long long num_slots, int* status, void* stream) {
+                                   void* k_pages, long long num_slots, int* status, void* stream, int interleaved) {
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens < 0 || heads <= 0 || dim <= 0 || rot < 0 || rank <= 0) return ULLM_ERR_BAD_SIZE;
   if (rot_dims < 0 || rot_dims > rot || rot_dims % 2 || (rot_dims > 0 && inv_freq == nullptr)) return ULLM_ERR_BAD_SIZE;
@@ -254,11 +356,38 @@ extern "C" int ullm_latent_prepare(int dtype, const void* q_full, const void* q_
   const dim3 grid(tokens), block(prep_threads(heads * rank / 4));
 #define LP_GO(T)                                                                                                  \
   return ullm_launch_kernel(latent_prepare_kernel<T>, grid, block, 0, st, (const T*)q_full, (const T*)q_lat,       \
-                            (const T*)dkv, (T*)q_out, tokens, heads, dim, rot, rank, rot_dims, w_c, eps, inv_freq, \
-                            positions, slot_mapping, (T*)k_pages, num_slots, status)
+                            (const T*)dkv, (T*)q_out, tokens, heads, dim, rot, rank, rot_dims, interleaved, w_c, eps,  \
+                            inv_freq, positions, slot_mapping, (T*)k_pages, num_slots, status)
   if (dtype == ULLM_DTYPE_F32) LP_GO(float);
   if (dtype == ULLM_DTYPE_BF16) LP_GO(__nv_bfloat16);
   if (dtype == ULLM_DTYPE_F16) LP_GO(__half);
 #undef LP_GO
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+// `wq` / `wk` null: no norm of q and k.  `rot_dims` 0: no rotation.  `q_head_scale` null: none.  `slot_mapping` null:
+// nothing is stored (q is still prepared).
+extern "C" int ullm_qkv_rows_prepare(int dtype, const void* qkv, long long stride, void* q_out, int tokens, int num_q,
+                                     int num_kv, int head_dim, int v_dim, const float* wq, const float* wk, float eps,
+                                     const float* inv_freq, int rot_dims, int interleaved, const int* positions,
+                                     const float* q_head_scale, int v_unit, const int* slot_mapping, void* k_pages,
+                                     void* v_pages, long long num_slots, int* status, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || num_q <= 0 || num_kv <= 0 || head_dim <= 0 || v_dim <= 0) return ULLM_ERR_BAD_SIZE;
+  if (stride < (long long)num_q * head_dim + (long long)num_kv * (head_dim + v_dim)) return ULLM_ERR_BAD_SIZE;
+  if ((wq == nullptr) != (wk == nullptr)) return ULLM_ERR_BAD_SIZE;
+  if (rot_dims < 0 || rot_dims > head_dim || rot_dims % 2) return ULLM_ERR_BAD_SIZE;
+  if (rot_dims > 0 && (inv_freq == nullptr || positions == nullptr)) return ULLM_ERR_BAD_SIZE;
+  if (rot_dims > ROWS_MAX_ROT) return ULLM_ERR_UNSUPPORTED;
+  if (tokens == 0) return ULLM_OK;
+  const dim3 grid(tokens), block(prep_threads(num_q * head_dim / 4));
+#define QRP_GO(T)                                                                                                    \
+  return ullm_launch_kernel(qkv_rows_prepare_kernel<T>, grid, block, 0, st, (const T*)qkv, stride, (T*)q_out, num_q,  \
+                            num_kv, head_dim, v_dim, wq, wk, eps, inv_freq, rot_dims, interleaved, positions,         \
+                            q_head_scale, v_unit, slot_mapping, (T*)k_pages, (T*)v_pages, num_slots, status)
+  if (dtype == ULLM_DTYPE_F32) QRP_GO(float);
+  if (dtype == ULLM_DTYPE_BF16) QRP_GO(__nv_bfloat16);
+  if (dtype == ULLM_DTYPE_F16) QRP_GO(__half);
+#undef QRP_GO
   return ULLM_ERR_BAD_DTYPE;
 }

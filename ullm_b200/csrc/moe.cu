@@ -1,7 +1,8 @@
 // Routed feed-forward (mixture of experts) without a host round trip:
 //
 //   moe_route     per token: scores from the 32-bit router logits (sigmoid, or softmax over the experts), the
-//                 `top` largest (ties: the lower index), their weights (the scores, optionally renormalized)
+//                 `top` largest (ties: the lower index), their weights (the scores, optionally renormalized);
+//                 with a `correction` per expert the CHOICE goes by score + correction, the weight stays the score
 //   moe_arrange   the (token, choice) pairs grouped by expert: offsets[E + 1], sorted[p] = pair at place p,
 //                 place[pair] = p
 //   moe_grouped_linear   for every expert e and every place p of it:  out[p] = f(W_e . (s_p * x[row(p)]))
@@ -9,7 +10,12 @@
 //                 out[p] = act(s_p * gate . x) * (s_p * up . x); s_p = the pair's weight when the weight
 //                 multiplies the expert's input, else 1
 //   moe_combine   y[t] = sum over the token's choices (in choice order) of c * rows[place], c = the weight when it
-//                 multiplies the expert's output, else 1
+//                 multiplies the expert's output, else 1.  A choice at or beyond `experts` (an expert without
+//                 tensors that passes its input) adds c * x[t]; a shared expert's rows, if given, are added times
+//                 sigmoid of one 32-bit number per token
+//
+// Gate activations of the grouped product: 0 silu(g) u, 1 gelu_tanh(g) u, 2 the clamped form
+// g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit).
 //
 // The grouped product is a tiled kernel with 32-bit accumulation for float32 and 16-bit storage alike; a block
 // finds its (expert, row tile) from the offsets, so the grid depends only on the step's size.
@@ -17,14 +23,16 @@
 
 #define MOE_MAX_TOP 16
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, int* __restrict__ choice, float* __restrict__ weight,
-                                 int tokens, int experts, int top, int softmax_scores, int renormalize) {
+__global__ void moe_route_kernel(const float* __restrict__ logits, long long logits_stride,
+                                 const float* __restrict__ correction, int* __restrict__ choice,
+                                 float* __restrict__ weight, int tokens, int experts, int top, int softmax_scores,
+                                 int renormalize) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= tokens) return;
-  const float* z = logits + (long long)t * experts;
+  const float* z = logits + (long long)t * logits_stride;
   float zmax = -INFINITY, zsum = 0.f;
   if (softmax_scores) {
     for (int e = lane; e < experts; e += 32) zmax = fmaxf(zmax, z[e]);
@@ -35,31 +43,35 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int* __restri
   int taken[MOE_MAX_TOP];
   float total = 0.f;
   for (int k = 0; k < top; ++k) {
-    float best = -INFINITY;
+    float best = -INFINITY, best_s = 0.f;  // the choice's rank (score + correction) and its score
     int best_e = 0x7fffffff;
     for (int e = lane; e < experts; e += 32) {
       bool used = false;
       for (int j = 0; j < k; ++j) used |= taken[j] == e;
       if (used) continue;
       const float s = softmax_scores ? expf(z[e] - zmax) / zsum : 1.f / (1.f + expf(-z[e]));
-      if (s > best || (s == best && e < best_e)) {
-        best = s;
+      const float rank = correction != nullptr ? s + correction[e] : s;
+      if (rank > best || (rank == best && e < best_e)) {
+        best = rank;
+        best_s = s;
         best_e = e;
       }
     }
     for (int o = 16; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
       const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
       if (ob > best || (ob == best && oe < best_e)) {
         best = ob;
+        best_s = os;
         best_e = oe;
       }
     }
     taken[k] = best_e;
-    total += best;
+    total += best_s;
     if (lane == 0) {
       choice[(long long)t * top + k] = best_e;
-      weight[(long long)t * top + k] = best;
+      weight[(long long)t * top + k] = best_s;
     }
   }
   if (renormalize && lane == 0)
@@ -101,6 +113,15 @@ __global__ void moe_arrange_kernel(const int* __restrict__ choice, int pairs, in
   }
 }
 
+__device__ __forceinline__ float moe_gate_act(int act, float g, float u, float limit, float alpha) {
+  if (act == 2) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-alpha * g)) * (u + 1.f);
+  }
+  return (act == 0 ? act_silu(g) : act_gelu_tanh(g)) * u;
+}
+
 #define MOE_BM 32
 #define MOE_BN 64
 #define MOE_BK 32
@@ -111,7 +132,7 @@ __global__ void __launch_bounds__(MOE_THREADS)
 moe_grouped_linear_kernel(const T* __restrict__ x, long long x_stride, const T* __restrict__ weights,
                           long long expert_stride, const int* __restrict__ offsets, const int* __restrict__ sorted,
                           const float* __restrict__ pair_weight, T* __restrict__ out, int experts, int top,
-                          int rows_from_pairs, int n_out, int k_dim, int act) {
+                          int rows_from_pairs, int n_out, int k_dim, int act, float limit, float alpha) {
   __shared__ float As[MOE_BK][MOE_BM + 1];
   __shared__ float Bs[GATED ? 2 : 1][MOE_BK][MOE_BN + 1];
   __shared__ int s_row[MOE_BM];
@@ -194,7 +215,7 @@ moe_grouped_linear_kernel(const T* __restrict__ x, long long x_stride, const T* 
       float v;
       if (GATED) {
         const float g = acc[0][i][j] * sc, u = acc[1][i][j] * sc;
-        v = (act == 0 ? act_silu(g) : act_gelu_tanh(g)) * u;
+        v = moe_gate_act(act, g, u, limit, alpha);
       } else {
         v = acc[0][i][j] * sc;
       }
@@ -244,7 +265,7 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
                        const __nv_bfloat16* __restrict__ weights, long long expert_stride,
                        const int* __restrict__ offsets, const int* __restrict__ sorted,
                        const float* __restrict__ pair_weight, __nv_bfloat16* __restrict__ out, int experts, int top,
-                       int rows_from_pairs, int n_out, int k_dim, int act) {
+                       int rows_from_pairs, int n_out, int k_dim, int act, float limit, float alpha) {
   constexpr int NB = GATED ? 2 : 1;
   constexpr int TILE = MMA_BM * MMA_BK * 2;  // bytes of one 64 x 64 tile
   extern __shared__ __align__(128) unsigned char moe_smem[];
@@ -351,7 +372,7 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
       for (int j = 0; j < 2; ++j) {
         if (GATED) {
           const float gt = acc[0][t][2 * h + j] * sc, up = acc[NB - 1][t][2 * h + j] * sc;
-          v[j] = (act == 0 ? act_silu(gt) : act_gelu_tanh(gt)) * up;
+          v[j] = moe_gate_act(act, gt, up, limit, alpha);
         } else {
           v[j] = acc[0][t][2 * h + j] * sc;
         }
@@ -363,17 +384,24 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
 
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __restrict__ place,
-                                   const float* __restrict__ pair_weight, T* __restrict__ y, int top, int cols) {
+                                   const float* __restrict__ pair_weight, T* __restrict__ y, int top, int cols,
+                                   const int* __restrict__ choice, int experts, const T* __restrict__ x,
+                                   long long x_stride, const T* __restrict__ shared_rows,
+                                   const float* __restrict__ shared_gate, long long gate_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const long long t = blockIdx.x;
+  float sg = 1.f;
+  if (shared_rows != nullptr && shared_gate != nullptr) sg = 1.f / (1.f + expf(-shared_gate[t * gate_stride]));
   for (int c = threadIdx.x; c < cols; c += blockDim.x) {
     float s = 0.f;
     for (int k = 0; k < top; ++k) {
       const long long pair = t * top + k;
-      const float v = to_f32(rows[(long long)place[pair] * cols + c]);
+      const bool passes = choice != nullptr && choice[pair] >= experts;  // an expert that is its input
+      const float v = passes ? to_f32(x[t * x_stride + c]) : to_f32(rows[(long long)place[pair] * cols + c]);
       s += pair_weight != nullptr ? pair_weight[pair] * v : v;
     }
+    if (shared_rows != nullptr) s += sg * to_f32(shared_rows[t * cols + c]);
     y[t * cols + c] = from_f32<T>(s);
   }
 }
@@ -382,13 +410,17 @@ static int g_moe_force_plain = 0;
 // 1: the grouped product never takes the tensor-core kernel (tests compare the two)
 extern "C" void ullm_moe_force_plain(int on) { g_moe_force_plain = on ? 1 : 0; }
 
-extern "C" int ullm_moe_route(const float* logits, int* choice, float* weight, int tokens, int experts, int top,
-                              int softmax_scores, int renormalize, void* stream) {
-  if (tokens < 0 || experts <= 0 || top <= 0) return ULLM_ERR_BAD_SIZE;
+// `logits_stride`: floats between two tokens' rows (the rows may hold further columns behind the experts');
+// `correction` (null: none): added to the scores for the choice only.
+extern "C" int ullm_moe_route(const float* logits, long long logits_stride, const float* correction, int* choice,
+                              float* weight, int tokens, int experts, int top, int softmax_scores, int renormalize,
+                              void* stream) {
+  if (tokens < 0 || experts <= 0 || top <= 0 || logits_stride < experts) return ULLM_ERR_BAD_SIZE;
   if (top > experts || top > MOE_MAX_TOP) return ULLM_ERR_UNSUPPORTED;
   if (tokens == 0) return ULLM_OK;
   return ullm_launch_kernel(moe_route_kernel, dim3((tokens + 3) / 4), dim3(128), 0, (cudaStream_t)stream, logits,
-                            choice, weight, tokens, experts, top, softmax_scores, renormalize);
+                            logits_stride, correction, choice, weight, tokens, experts, top, softmax_scores,
+                            renormalize);
 }
 
 extern "C" int ullm_moe_arrange(const int* choice, int pairs, int experts, int* offsets, int* sorted, int* place,
@@ -403,16 +435,16 @@ template <typename T>
 static int grouped_launch(const void* x, long long x_stride, const void* weights, long long expert_stride,
                           const int* offsets, const int* sorted, const float* pair_weight, void* out, int pairs,
                           int experts, int top, int rows_from_pairs, int n_out, int k_dim, int gated, int act,
-                          cudaStream_t st) {
+                          float limit, float alpha, cudaStream_t st) {
   const int row_tiles = (pairs + MOE_BM - 1) / MOE_BM + experts;  // an upper bound whatever the routing
   const dim3 grid((n_out + MOE_BN - 1) / MOE_BN, row_tiles), block(MOE_THREADS);
   if (gated)
     return ullm_launch_kernel(moe_grouped_linear_kernel<T, true>, grid, block, 0, st, (const T*)x, x_stride,
                               (const T*)weights, expert_stride, offsets, sorted, pair_weight, (T*)out, experts, top,
-                              rows_from_pairs, n_out, k_dim, act);
+                              rows_from_pairs, n_out, k_dim, act, limit, alpha);
   return ullm_launch_kernel(moe_grouped_linear_kernel<T, false>, grid, block, 0, st, (const T*)x, x_stride,
                             (const T*)weights, expert_stride, offsets, sorted, pair_weight, (T*)out, experts, top,
-                            rows_from_pairs, n_out, k_dim, act);
+                            rows_from_pairs, n_out, k_dim, act, limit, alpha);
 }
 
 // x: rows of k_dim elements (stride x_stride); row of place p = token of its pair (rows_from_pairs) or p itself.
@@ -420,15 +452,17 @@ static int grouped_launch(const void* x, long long x_stride, const void* weights
 extern "C" int ullm_moe_grouped_linear(int dtype, const void* x, long long x_stride, const void* weights,
                                        long long expert_stride, const int* offsets, const int* sorted,
                                        const float* pair_weight, void* out, int pairs, int experts, int top,
-                                       int rows_from_pairs, int n_out, int k_dim, int gated, int act, void* stream) {
+                                       int rows_from_pairs, int n_out, int k_dim, int gated, int act, float limit,
+                                       float alpha, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (pairs < 0 || experts <= 0 || top <= 0 || n_out <= 0 || k_dim <= 0) return ULLM_ERR_BAD_SIZE;
-  if (gated && act != 0 && act != 1) return ULLM_ERR_UNSUPPORTED;
+  if (gated && (act < 0 || act > 2)) return ULLM_ERR_UNSUPPORTED;
+  if (gated && act == 2 && !(limit > 0.f)) return ULLM_ERR_BAD_SIZE;
   if (pairs == 0) return ULLM_OK;
   if ((pairs + MOE_BM - 1) / MOE_BM + experts > 65535) return ULLM_ERR_BAD_SIZE;
   if (dtype == ULLM_DTYPE_F32)
     return grouped_launch<float>(x, x_stride, weights, expert_stride, offsets, sorted, pair_weight, out, pairs,
-                                 experts, top, rows_from_pairs, n_out, k_dim, gated, act, st);
+                                 experts, top, rows_from_pairs, n_out, k_dim, gated, act, limit, alpha, st);
   if (dtype == ULLM_DTYPE_BF16) {
     const bool tensor_cores = !g_moe_force_plain && k_dim % 8 == 0 && x_stride % 8 == 0 && n_out % 2 == 0 &&
                               (uintptr_t)x % 16 == 0 && (uintptr_t)weights % 16 == 0 && (uintptr_t)out % 4 == 0 &&
@@ -450,36 +484,45 @@ extern "C" int ullm_moe_grouped_linear(int dtype, const void* x, long long x_str
       if (gated)
         return ullm_launch_kernel(moe_grouped_mma_kernel<true>, grid, block, smem, st, (const __nv_bfloat16*)x, x_stride,
                                   (const __nv_bfloat16*)weights, expert_stride, offsets, sorted, pair_weight,
-                                  (__nv_bfloat16*)out, experts, top, rows_from_pairs, n_out, k_dim, act);
+                                  (__nv_bfloat16*)out, experts, top, rows_from_pairs, n_out, k_dim, act, limit, alpha);
       return ullm_launch_kernel(moe_grouped_mma_kernel<false>, grid, block, smem, st, (const __nv_bfloat16*)x, x_stride,
                                 (const __nv_bfloat16*)weights, expert_stride, offsets, sorted, pair_weight,
-                                (__nv_bfloat16*)out, experts, top, rows_from_pairs, n_out, k_dim, act);
+                                (__nv_bfloat16*)out, experts, top, rows_from_pairs, n_out, k_dim, act, limit, alpha);
     }
     return grouped_launch<__nv_bfloat16>(x, x_stride, weights, expert_stride, offsets, sorted, pair_weight, out,
-                                         pairs, experts, top, rows_from_pairs, n_out, k_dim, gated, act, st);
+                                         pairs, experts, top, rows_from_pairs, n_out, k_dim, gated, act, limit, alpha, st);
   }
   if (dtype == ULLM_DTYPE_F16)
     return grouped_launch<__half>(x, x_stride, weights, expert_stride, offsets, sorted, pair_weight, out, pairs,
-                                  experts, top, rows_from_pairs, n_out, k_dim, gated, act, st);
+                                  experts, top, rows_from_pairs, n_out, k_dim, gated, act, limit, alpha, st);
   return ULLM_ERR_BAD_DTYPE;
 }
 
+// `choice` with `experts` and `x` (null: every choice has rows): a choice >= experts adds the weight times the
+// token's row of x.  `shared_rows` (null: none): added times sigmoid(shared_gate[t * gate_stride]) (gate null: 1).
 extern "C" int ullm_moe_combine(int dtype, const void* rows, const int* place, const float* pair_weight, void* y,
-                                int tokens, int top, int cols, void* stream) {
+                                int tokens, int top, int cols, const int* choice, int experts, const void* x,
+                                long long x_stride, const void* shared_rows, const float* shared_gate,
+                                long long gate_stride, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens < 0 || top <= 0 || cols <= 0) return ULLM_ERR_BAD_SIZE;
+  if (choice != nullptr && (x == nullptr || x_stride < cols || experts < 0)) return ULLM_ERR_BAD_SIZE;
   if (tokens == 0) return ULLM_OK;
   int threads = 32;
   while (threads < 256 && threads * 4 < cols) threads <<= 1;
   const dim3 grid(tokens), block(threads);
   if (dtype == ULLM_DTYPE_F32)
     return ullm_launch_kernel(moe_combine_kernel<float>, grid, block, 0, st, (const float*)rows, place, pair_weight,
-                              (float*)y, top, cols);
+                              (float*)y, top, cols, choice, experts, (const float*)x, x_stride,
+                              (const float*)shared_rows, shared_gate, gate_stride);
   if (dtype == ULLM_DTYPE_BF16)
     return ullm_launch_kernel(moe_combine_kernel<__nv_bfloat16>, grid, block, 0, st, (const __nv_bfloat16*)rows,
-                              place, pair_weight, (__nv_bfloat16*)y, top, cols);
+                              place, pair_weight, (__nv_bfloat16*)y, top, cols, choice, experts,
+                              (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)shared_rows, shared_gate,
+                              gate_stride);
   if (dtype == ULLM_DTYPE_F16)
     return ullm_launch_kernel(moe_combine_kernel<__half>, grid, block, 0, st, (const __half*)rows, place, pair_weight,
-                              (__half*)y, top, cols);
+                              (__half*)y, top, cols, choice, experts, (const __half*)x, x_stride,
+                              (const __half*)shared_rows, shared_gate, gate_stride);
   return ULLM_ERR_BAD_DTYPE;
 }

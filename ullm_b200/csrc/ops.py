@@ -268,14 +268,17 @@ class Kernels:
             "ullm_xielu": [I, P, P, LL, P, P],
             "ullm_kv_shared_prepare": [I, P, LL, I, I, I, P, P, F, P, P, P, LL, P, P],
             "ullm_pool_blocks": [I, P, P, P, P, I, I, LL, P, P, I, I, P, LL, P, P, I, I, P, P],
-            "ullm_latent_prepare": [I, P, P, P, P, I, I, I, I, I, I, P, F, P, P, P, P, LL, P, P],
+            "ullm_latent_prepare": [I, P, P, P, P, I, I, I, I, I, I, P, F, P, P, P, P, LL, P, P, I],
+            "ullm_qkv_rows_prepare": [I, P, LL, P, I, I, I, I, I, P, P, F, P, I, I, P, P, I, P, P, P, LL, P, P],
+            "ullm_concat_rows_f32": [I, P, P, P, I, I, I, P],
+            "ullm_sigmoid_gate": [I, P, P, LL, I, I, P],
             "ullm_mingru": [I, P, LL, I, I, I, P, P, P, LL, P, P, P, P, LL, F, I, I, I, P, P],
             "ullm_gla_recurrence": [I, P, LL, I, I, I, P, LL, P, F, F, P, LL, P, P, P, P, I, I, I, I, I, I, P, P],
             "ullm_head_norm_gate": [I, P, P, LL, P, P, I, I, I, F, I, I, P],
-            "ullm_moe_route": [P, P, P, I, I, I, I, I, P],
+            "ullm_moe_route": [P, LL, P, P, P, I, I, I, I, I, P],
             "ullm_moe_arrange": [P, I, I, P, P, P, P],
-            "ullm_moe_grouped_linear": [I, P, LL, P, LL, P, P, P, P, I, I, I, I, I, I, I, I, P],
-            "ullm_moe_combine": [I, P, P, P, P, I, I, I, P],
+            "ullm_moe_grouped_linear": [I, P, LL, P, LL, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P],
+            "ullm_moe_combine": [I, P, P, P, P, I, I, I, P, I, P, LL, P, P, LL, P],
             "ullm_argmax": [P, LL, I, I, P, P],
             "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P, P, P],
         }
@@ -846,17 +849,19 @@ class Kernels:
     # -- norms on both sides of a sub-layer, on a 32-bit stream -------------------
     @_timed("add_rmsnorm")
     def norm_add_norm(self, stream, a=None, weight=None, eps: float = 0.0, mult: float = 1.0, center: bool = False,
-                      extra_rows=None, extra_vec=None, next_norm=None):
+                      extra_rows=None, extra_vec=None, next_norm=None, plain: bool = False):
         """stream (float32, in place) += mult * weight * n(a), then += extra_rows, then += extra_vec (each part
         optional); `next_norm` = (weight2, eps2, center2, out): out = weight2 * n2(stream) rounded to out's dtype.
-        n(v) = v / sqrt(mean(v^2) + eps), with `center` (v - mean) / sqrt(mean((v - mean)^2) + eps)."""
+        n(v) = v / sqrt(mean(v^2) + eps), with `center` (v - mean) / sqrt(mean((v - mean)^2) + eps); with `plain`
+        n(v) = v (a is only scaled channel by channel; `weight` None: not even that)."""
         _need(stream, "stream", torch.float32)
         rows, cols = stream.shape
         if a is not None:
             _need(a, "a")
-            _need(weight, "weight", torch.float32)
-            if a.shape != stream.shape or weight.numel() != cols:
-                raise KernelError(f"norm_add_norm: a {tuple(a.shape)}, stream {tuple(stream.shape)}, weight {tuple(weight.shape)}")
+            if weight is not None or not plain:
+                _need(weight, "weight", torch.float32)
+            if a.shape != stream.shape or (weight is not None and weight.numel() != cols):
+                raise KernelError(f"norm_add_norm: a {tuple(a.shape)}, stream {tuple(stream.shape)}")
         if extra_rows is not None:
             _need(extra_rows, "extra_rows", torch.float32)
             if extra_rows.shape != stream.shape:
@@ -875,7 +880,7 @@ class Kernels:
                 raise KernelError("norm_add_norm: the next norm's shapes differ")
         self._check(self.lib.ullm_norm_add_norm(
             _DT[a.dtype] if a is not None else 0, _ptr(a), _ptr(stream), _ptr(weight), rows, cols, float(eps), float(mult),
-            int(bool(center)), _ptr(extra_rows), _ptr(extra_vec), _ptr(w2), float(eps2), int(bool(center2)),
+            2 if plain else int(bool(center)), _ptr(extra_rows), _ptr(extra_vec), _ptr(w2), float(eps2), int(bool(center2)),
             _DT[out.dtype] if out is not None else 0, _ptr(out), _stream()), f"norm_add_norm (row length {cols})")
 
     @_timed("add_rmsnorm")
@@ -963,11 +968,12 @@ class Kernels:
 
     @_timed("qk_norm_rope_store")
     def latent_prepare(self, q_full, q_lat, dkv, q_out, heads: int, dim: int, rot: int, rank: int, rot_dims: int, c_w,
-                       eps: float, inv_freq, positions, slot_mapping, k_pages):
+                       eps: float, inv_freq, positions, slot_mapping, k_pages, interleaved: bool = True):
         """Latent attention, absorbed form.  q_full [T, heads x (dim + rot)], q_lat [heads, T, rank] (each head's
         unrotated query times its key up-projection), dkv [T, rank + rot].  Leaves q_out [T, heads x (rank + rot)]
         = [q_lat | rotated q_rot] per head and the key row [RMSnorm(dkv[:rank]) x c_w | rotated dkv[rank:]] in
-        `k_pages` at the tokens' slots.  Neighbouring dimensions (2i, 2i + 1) below `rot_dims` are rotated."""
+        `k_pages` at the tokens' slots.  Neighbouring dimensions (2i, 2i + 1) below `rot_dims` are rotated, or
+        without `interleaved` the dimensions (i, i + rot_dims / 2)."""
         T = dkv.shape[0]
         for t, n in ((q_full, "q_full"), (q_lat, "q_lat"), (dkv, "dkv"), (q_out, "q_out"), (k_pages, "k_pages")):
             _need(t, n, dkv.dtype)
@@ -985,7 +991,70 @@ class Kernels:
         self._check(self.lib.ullm_latent_prepare(
             _DT[dkv.dtype], _ptr(q_full), _ptr(q_lat), _ptr(dkv), _ptr(q_out), T, heads, dim, rot, rank, rot_dims,
             _ptr(c_w), float(eps), _ptr(inv_freq), _ptr(positions), _ptr(slot_mapping), _ptr(k_pages),
-            k_pages.numel() // (rank + rot), _ptr(self.status), _stream()), "latent_prepare")
+            k_pages.numel() // (rank + rot), _ptr(self.status), _stream(), int(bool(interleaved))), "latent_prepare")
+
+    @_timed("qk_norm_rope_store")
+    def qkv_rows_prepare(self, qkv, q_out, num_q: int, num_kv: int, head_dim: int, v_dim: int, positions, slot_mapping,
+                         k_pages, v_pages, *, q_w=None, k_w=None, eps: float = 0.0, inv_freq=None, rotary_dim: int = 0,
+                         interleaved: bool = False, q_head_scale=None, value_unit_norm: bool = False):
+        """qkv [T, q | k | v] as projected.  q and k pass an RMS norm over the WHOLE projection (weights `q_w`
+        [num_q * head_dim], `k_w` [num_kv * head_dim]; None: no norm), then the first `rotary_dim` dimensions of every
+        head turn (neighbours with `interleaved`, else halves) by computed angles; q is multiplied head by head by
+        `q_head_scale` [num_q] and goes to `q_out`, k to the key pages; v, with `value_unit_norm` every head divided by
+        its root mean square (eps, no weight), to the value pages."""
+        _need(qkv, "qkv", contiguous=False)
+        _need(q_out, "q_out", qkv.dtype)
+        T = qkv.shape[0]
+        W = num_q * head_dim + num_kv * (head_dim + v_dim)
+        if qkv.stride(1) != 1 or qkv.shape[1] < W or q_out.shape != (T, num_q * head_dim):
+            raise KernelError(f"qkv_rows_prepare: qkv {tuple(qkv.shape)}, q_out {tuple(q_out.shape)}")
+        if (q_w is None) != (k_w is None):
+            raise KernelError("qkv_rows_prepare: the norm weights of q and k come together")
+        for t_, n_, want in ((q_w, "q norm weight", num_q * head_dim), (k_w, "k norm weight", num_kv * head_dim),
+                             (q_head_scale, "head factors", num_q), (inv_freq, "inv_freq", rotary_dim // 2)):
+            if t_ is not None:
+                _need(t_, n_, torch.float32)
+                if t_.numel() < want:
+                    raise KernelError(f"qkv_rows_prepare: {n_} holds {t_.numel()} values, {want} are needed")
+        if rotary_dim > 0:
+            if inv_freq is None:
+                raise KernelError("qkv_rows_prepare: a rotation needs its frequency table")
+            _need(positions, "positions", torch.int32)
+        num_slots = 0
+        if slot_mapping is not None:
+            _need(slot_mapping, "slot_mapping", torch.int32)
+            _need(k_pages, "k_pages", qkv.dtype)
+            _need(v_pages, "v_pages", qkv.dtype)
+            if k_pages.shape[-2:] != (num_kv, head_dim) or v_pages.shape[-2:] != (num_kv, v_dim):
+                raise KernelError(f"qkv_rows_prepare: pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)}")
+            num_slots = k_pages.numel() // (num_kv * head_dim)
+        self._check(self.lib.ullm_qkv_rows_prepare(
+            _DT[qkv.dtype], _ptr(qkv), qkv.stride(0), _ptr(q_out), T, num_q, num_kv, head_dim, v_dim, _ptr(q_w), _ptr(k_w),
+            float(eps), _ptr(inv_freq), int(rotary_dim), int(bool(interleaved)), _ptr(positions), _ptr(q_head_scale),
+            int(bool(value_unit_norm)), _ptr(slot_mapping), _ptr(k_pages), _ptr(v_pages), num_slots, _ptr(self.status),
+            _stream()), f"qkv_rows_prepare (head_dim {head_dim})")
+
+    @_timed("add_rmsnorm")
+    def concat_rows_f32(self, a, b, out):
+        """out[t] = [a[t] | b[t]] rounded to out's dtype; a, b float32."""
+        _need(a, "a", torch.float32)
+        _need(b, "b", torch.float32)
+        _need(out, "out")
+        T = a.shape[0]
+        if b.shape[0] != T or out.shape != (T, a.shape[1] + b.shape[1]):
+            raise KernelError(f"concat_rows_f32: a {tuple(a.shape)}, b {tuple(b.shape)}, out {tuple(out.shape)}")
+        self._check(self.lib.ullm_concat_rows_f32(_DT[out.dtype], _ptr(a), _ptr(b), _ptr(out), T, a.shape[1], b.shape[1],
+                                                  _stream()), "concat_rows_f32")
+
+    @_timed("act_mul")
+    def sigmoid_gate(self, a, g):
+        """a (in place) *= sigmoid(g), element by element; g [T, cols] may be a column range of wider rows."""
+        _need(a, "a")
+        _need(g, "g", a.dtype, contiguous=False)
+        if g.shape != a.shape or g.stride(1) != 1:
+            raise KernelError(f"sigmoid_gate: a {tuple(a.shape)}, g {tuple(g.shape)}")
+        self._check(self.lib.ullm_sigmoid_gate(_DT[a.dtype], _ptr(a), _ptr(g), g.stride(0), a.shape[0], a.shape[1],
+                                               _stream()), "sigmoid_gate")
 
     @_timed("attention")
     def windowed_attention(self, q, out, k_pages, v_pages, block_table, req_slots, cu_q, kv_len, token_req, num_q: int,
@@ -1336,15 +1405,24 @@ class Kernels:
 
     # -- routed experts -----------------------------------------------------------
     @_timed("moe")
-    def moe_route(self, logits, choice, weight, top: int, softmax_scores: bool = False, renormalize: bool = False):
+    def moe_route(self, logits, choice, weight, top: int, softmax_scores: bool = False, renormalize: bool = False,
+                  correction=None, experts: int | None = None):
+        """`experts`: the router's outputs, when the logits' rows hold further columns behind them.  `correction`
+        (float32 [experts]): added to the scores for the choice; the weights stay the scores."""
         _need(logits, "router logits", torch.float32)
         _need(choice, "choice", torch.int32)
         _need(weight, "weight", torch.float32)
-        T, E = logits.shape
-        if choice.numel() < T * top or weight.numel() < T * top:
+        T = logits.shape[0]
+        E = logits.shape[1] if experts is None else int(experts)
+        if choice.numel() < T * top or weight.numel() < T * top or E > logits.shape[1]:
             raise KernelError("moe_route: outputs too small")
-        self._check(self.lib.ullm_moe_route(_ptr(logits), _ptr(choice), _ptr(weight), T, E, top, int(softmax_scores),
-                                            int(renormalize), _stream()), f"moe_route ({E} experts, top {top})")
+        if correction is not None:
+            _need(correction, "correction", torch.float32)
+            if correction.numel() != E:
+                raise KernelError(f"moe_route: {correction.numel()} corrections for {E} router outputs")
+        self._check(self.lib.ullm_moe_route(_ptr(logits), logits.stride(0), _ptr(correction), _ptr(choice), _ptr(weight), T,
+                                            E, top, int(softmax_scores), int(renormalize), _stream()),
+                    f"moe_route ({E} experts, top {top})")
 
     @_timed("moe")
     def moe_arrange(self, choice, pairs: int, experts: int, offsets, sorted_pairs, place):
@@ -1357,9 +1435,9 @@ class Kernels:
 
     @_timed("moe", lambda x, weights, *r: weights.numel() * weights.element_size())
     def moe_grouped_linear(self, x, weights, offsets, sorted_pairs, pair_weight, out, top: int, rows_from_pairs: bool,
-                           gated: bool, act: int = 0):
+                           gated: bool, act: int = 0, limit: float = 0.0, alpha: float = 1.0):
         """out[p] = W_e . x[row(p)] for every place p of every expert e (see csrc/moe.cu); weights
-        [experts, (2 if gated) * n_out, k]."""
+        [experts, (2 if gated) * n_out, k].  `act` 2: the clamped gate with `limit` and `alpha`."""
         _need(x, "x")
         _need(weights, "expert weights", x.dtype)
         _need(out, "out", x.dtype)
@@ -1371,7 +1449,8 @@ class Kernels:
             _need(pair_weight, "pair weights", torch.float32)
         self._check(self.lib.ullm_moe_grouped_linear(
             _DT[x.dtype], _ptr(x), x.stride(0), _ptr(weights), weights.stride(0), _ptr(offsets), _ptr(sorted_pairs),
-            _ptr(pair_weight), _ptr(out), pairs, E, top, int(rows_from_pairs), n_out, K, int(gated), act, _stream()),
+            _ptr(pair_weight), _ptr(out), pairs, E, top, int(rows_from_pairs), n_out, K, int(gated), act, float(limit),
+            float(alpha), _stream()),
             f"moe_grouped_linear ({E} experts, {N} x {K})")
 
     def moe_force_plain(self, on: bool) -> None:
@@ -1379,15 +1458,38 @@ class Kernels:
         self.lib.ullm_moe_force_plain(1 if on else 0)
 
     @_timed("moe")
-    def moe_combine(self, rows, place, pair_weight, y, top: int):
+    def moe_combine(self, rows, place, pair_weight, y, top: int, passing=None, shared=None):
+        """`passing` = (choice, experts, x): a choice at or beyond `experts` adds its weight times the token's row of
+        x [T, cols] instead of an expert's row.  `shared` = (rows [T, cols], gate or None): added to every token,
+        times sigmoid(gate[t]) (float32, one number per token, any row stride)."""
         _need(rows, "rows")
         _need(place, "place", torch.int32)
         _need(y, "y", rows.dtype)
         T, C = y.shape
         if rows.shape[1] != C or rows.shape[0] < T * top:
             raise KernelError("moe_combine: shapes differ")
+        choice = x = s_rows = s_gate = None
+        experts = x_stride = g_stride = 0
+        if passing is not None:
+            choice, experts, x = passing
+            _need(choice, "choice", torch.int32)
+            _need(x, "x", rows.dtype, contiguous=False)
+            if x.shape != (T, C) or x.stride(1) != 1 or choice.numel() < T * top:
+                raise KernelError("moe_combine: the passing experts' input does not fit")
+            x_stride = x.stride(0)
+        if shared is not None:
+            s_rows, s_gate = shared
+            _need(s_rows, "shared rows", rows.dtype)
+            if s_rows.shape != (T, C):
+                raise KernelError("moe_combine: the shared expert's rows do not fit")
+            if s_gate is not None:
+                _need(s_gate, "shared gate", torch.float32, contiguous=False)
+                if s_gate.shape[0] != T:
+                    raise KernelError("moe_combine: one gate number per token")
+                g_stride = s_gate.stride(0)
         self._check(self.lib.ullm_moe_combine(_DT[y.dtype], _ptr(rows), _ptr(place), _ptr(pair_weight), _ptr(y), T, top, C,
-                                              _stream()), "moe_combine")
+                                              _ptr(choice), int(experts), _ptr(x), x_stride, _ptr(s_rows), _ptr(s_gate),
+                                              g_stride, _stream()), "moe_combine")
 
     def check_attention_sizes(self, *a):
         check_attention_sizes(*a)

@@ -8,9 +8,10 @@
 //   xielu           out = round(act(in)), act(z) = softplus(p) z^2 + z / 2 for z > 0,
 //                                          (1/2 + softplus(q)) (e^z - 1 - z) + z / 2 otherwise
 //
-// n(v) = v / sqrt(mean(v^2) + eps), or with `center` (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps): the
+// n(v) = v / sqrt(mean(v^2) + eps), or with `center` = 1 (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps): the
 // variance is the mean of the squared deviations, formed in a second pass over the row, which waits in shared
-// memory.  Sums, means and the stream are 32-bit; one rounding at each store.  One block per row.
+// memory.  `center` = 2 for the added operand: n(v) = v, so stream[t] += mult * w * a[t] (a scale per channel on a
+// sub-layer's output; w null: no scale), the arrangement of a pre-norm layer on a 32-bit stream.  Sums, means and the stream are 32-bit; one rounding at each store.  One block per row.
 #include "common.cuh"
 
 #define SN_MAX_SMEM (160 * 1024)
@@ -50,11 +51,12 @@ __global__ void norm_add_norm_kernel(const TA* __restrict__ a, float* __restrict
   if (a != nullptr) {
     for (int c = threadIdx.x; c < cols; c += blockDim.x) row_a[c] = to_f32(a[base + c]);
     __syncthreads();
-    rstd = row_rstd(row_a, cols, center != 0, eps, scratch, &mean);
+    rstd = 1.f;
+    if (center != 2) rstd = row_rstd(row_a, cols, center != 0, eps, scratch, &mean);
   }
   for (int c = threadIdx.x; c < cols; c += blockDim.x) {
     float s = stream[base + c];
-    if (a != nullptr) s += mult * ((row_a[c] - mean) * rstd * w[c]);
+    if (a != nullptr) s += mult * ((row_a[c] - mean) * rstd * (w != nullptr ? w[c] : 1.f));
     if (extra_rows != nullptr) s += extra_rows[base + c];
     if (extra_vec != nullptr) s += extra_vec[c];
     stream[base + c] = s;
@@ -143,7 +145,8 @@ extern "C" int ullm_norm_add_norm(int a_dtype, const void* a, float* stream, con
                                   void* out, void* stream_handle) {
   cudaStream_t st = (cudaStream_t)stream_handle;
   if (rows < 0 || cols <= 0) return ULLM_ERR_BAD_SIZE;
-  if ((a != nullptr && w == nullptr) || (out != nullptr && w2 == nullptr)) return ULLM_ERR_BAD_SIZE;
+  if ((a != nullptr && w == nullptr && center != 2) || (out != nullptr && w2 == nullptr)) return ULLM_ERR_BAD_SIZE;
+  if (center < 0 || center > 2 || center2 < 0 || center2 > 1) return ULLM_ERR_BAD_SIZE;
   if (rows == 0) return ULLM_OK;
 #define SN_GO(TA, TO)                                                                                              \
   return norm_add_norm_launch<TA, TO>(a, stream, w, rows, cols, eps, mult, center, extra_rows, extra_vec, w2, eps2, \

@@ -6,6 +6,8 @@
 //   norm_scale_add_norm   the same, and out[t] = the NEXT norm of the updated stream[t]
 //   rmsnorm_rows_f32  out[r] = round(w * s / sqrt(mean(s^2) + eps)), s = stream[rows[r]]
 //   cast_rows_f32     copy = round(stream)
+//   concat_rows_f32   out[t] = round([a[t] | b[t]]): two 32-bit row sets side by side as one product's operand
+//   sigmoid_gate      a[t] *= sigmoid(g[t]), element by element (g with a row stride of its own)
 //   gated_add_f32     stream[t] += sigmoid(g1[t] + b1) * a[t] (+ sigmoid(g2[t] + b2) * f[t]),       copy[t] = round(stream[t])
 //   side_gate_mul     out[t] = gelu_tanh(s[t]) * table[id[t]][offset .. offset + cols)
 //   softcap_f32       x = cap * tanh(x / cap), in place
@@ -127,6 +129,28 @@ __global__ void cast_rows_f32_kernel(const float* __restrict__ in, T* __restrict
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     out[i] = from_f32<T>(in[i]);
+}
+
+template <typename T>
+__global__ void concat_rows_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out,
+                                       int cols_a, int cols_b) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  T* o = out + t * (cols_a + cols_b);
+  for (int c = threadIdx.x; c < cols_a; c += blockDim.x) o[c] = from_f32<T>(a[t * cols_a + c]);
+  for (int c = threadIdx.x; c < cols_b; c += blockDim.x) o[cols_a + c] = from_f32<T>(b[t * cols_b + c]);
+}
+
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ a, const T* __restrict__ g, long long g_stride, int cols) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float z = to_f32(g[t * g_stride + c]);
+    a[t * cols + c] = from_f32<T>(to_f32(a[t * cols + c]) / (1.f + expf(-z)));
+  }
 }
 
 // Two sub-layers that read the same normed rows and are added to the stream together, each through a gate:
@@ -347,4 +371,37 @@ extern "C" int ullm_softcap_f32(float* x, long long n, float cap, void* stream_h
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   return ullm_launch_kernel(softcap_f32_kernel, dim3((int)blocks), dim3(256), 0, st, x, n, cap);
+}
+
+extern "C" int ullm_concat_rows_f32(int dtype, const float* a, const float* b, void* out, int rows, int cols_a,
+                                    int cols_b, void* stream_handle) {
+  cudaStream_t st = (cudaStream_t)stream_handle;
+  if (rows < 0 || cols_a <= 0 || cols_b <= 0) return ULLM_ERR_BAD_SIZE;
+  if (rows == 0) return ULLM_OK;
+  const dim3 grid(rows), block(row_threads(cols_a + cols_b));
+  if (dtype == ULLM_DTYPE_F32)
+    return ullm_launch_kernel(concat_rows_f32_kernel<float>, grid, block, 0, st, a, b, (float*)out, cols_a, cols_b);
+  if (dtype == ULLM_DTYPE_BF16)
+    return ullm_launch_kernel(concat_rows_f32_kernel<__nv_bfloat16>, grid, block, 0, st, a, b, (__nv_bfloat16*)out,
+                              cols_a, cols_b);
+  if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(concat_rows_f32_kernel<__half>, grid, block, 0, st, a, b, (__half*)out, cols_a, cols_b);
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+extern "C" int ullm_sigmoid_gate(int dtype, void* a, const void* g, long long g_stride, int rows, int cols,
+                                 void* stream_handle) {
+  cudaStream_t st = (cudaStream_t)stream_handle;
+  if (rows < 0 || cols <= 0 || g_stride < cols) return ULLM_ERR_BAD_SIZE;
+  if (rows == 0) return ULLM_OK;
+  const dim3 grid(rows), block(row_threads(cols));
+  if (dtype == ULLM_DTYPE_F32)
+    return ullm_launch_kernel(sigmoid_gate_kernel<float>, grid, block, 0, st, (float*)a, (const float*)g, g_stride, cols);
+  if (dtype == ULLM_DTYPE_BF16)
+    return ullm_launch_kernel(sigmoid_gate_kernel<__nv_bfloat16>, grid, block, 0, st, (__nv_bfloat16*)a,
+                              (const __nv_bfloat16*)g, g_stride, cols);
+  if (dtype == ULLM_DTYPE_F16)
+    return ullm_launch_kernel(sigmoid_gate_kernel<__half>, grid, block, 0, st, (__half*)a, (const __half*)g, g_stride,
+                              cols);
+  return ULLM_ERR_BAD_DTYPE;
 }

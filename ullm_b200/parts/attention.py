@@ -50,6 +50,9 @@ class PagedAttention(Mixer):
         value_mix: str | None = None,
         unit_norm_after_rotation: bool = False,
         norm_eps: float = 0.0,
+        whole_norm: bool = False,
+        value_unit_norm: bool = False,
+        head_temperature: bool = False,
     ):
         """`value_dim`: head size of the values and of the output (default: `head_dim`).  `window` with
         `keep_first`: position i sees j <= i if i - j < window or j < keep_first.  `own_kv` False: the mixer has
@@ -68,7 +71,15 @@ class PagedAttention(Mixer):
         "mix": v <- (1 - lambda) v + lambda v_first with the scalar `vmix` (what goes to the cache is the blend); both kinds
         declare the scalar.  `unit_norm_after_rotation`: q and k are divided by their root mean square over the
         head (eps `norm_eps`, no weight) behind the rotation.  A position of kind `rope_computed` (angles computed
-        in the kernel, optional frequency scaling) also takes this path."""
+        in the kernel, optional frequency scaling) also takes this path.
+
+        Three more, prepared by csrc/attention_prep_shared.cu (`qkv_rows_prepare`) in front of the same attention
+        kernels.  `whole_norm`: the q/k norm (`qk_norm`) runs over the WHOLE projection, all heads at once, with a
+        weight per channel (`q_norm` [heads * head_dim], `k_norm` [kv heads * head_dim]), before the rotation.
+        `value_unit_norm`: every head's value is divided by its root mean square (eps `norm_eps`, no weight); the
+        cache holds it so.  `head_temperature`: the scores of head h are multiplied by the learned number `temp`[h]
+        (it is folded into the prepared queries in 32-bit).  With any of them a `rope_computed` position may say
+        `interleaved=True` (neighbouring dimensions turn together)."""
         super().__init__()
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is no multiple of num_kv_heads={num_kv_heads}")
@@ -90,6 +101,17 @@ class PagedAttention(Mixer):
         self.value_mix = value_mix
         self.unit_norm_after_rotation = bool(unit_norm_after_rotation)
         self.norm_eps = float(norm_eps)
+        self.whole_norm = bool(whole_norm)
+        self.value_unit_norm = bool(value_unit_norm)
+        self.head_temperature = bool(head_temperature)
+        # the form that `qkv_rows_prepare` prepares
+        self.rows_form = self.whole_norm or self.value_unit_norm or self.head_temperature
+        if self.rows_form and (conv_taps or value_mix or unit_norm_after_rotation or talking_heads or qkv_bias
+                               or not own_kv or keep_first):
+            raise ValueError("whole_norm / value_unit_norm / head_temperature do not combine with the convolution, value "
+                             "mixing, the norm behind the rotation, mixed heads, biases, kept tokens or borrowed keys")
+        if self.whole_norm and qk_norm is None:
+            raise ValueError("whole_norm needs the norm's spec (qk_norm)")
         if self.conv_taps < 0 or self.conv_taps > 32:
             raise ValueError(f"conv_taps={conv_taps}: the convolution kernel takes 1 to 32 taps (0: none)")
         if self.score_cap is not None and self.score_cap <= 0:
@@ -100,17 +122,30 @@ class PagedAttention(Mixer):
             raise ValueError("a mixer without key / value projections has no values to convolve or to mix")
         n = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight", q_bias="q_proj.bias",
                  k_bias="k_proj.bias", v_bias="v_proj.bias", q_norm="q_norm.", k_norm="k_norm.",
-                 q_conv="q_proj.conv", k_conv="k_proj.conv", v_conv="v_proj.conv", talk="talk", vmix="vmix")
+                 q_conv="q_proj.conv", k_conv="k_proj.conv", v_conv="v_proj.conv", talk="talk", vmix="vmix",
+                 temp="temp")
         n.update(names or {})
         self.names = n
         self.q_size = num_heads * head_dim
         self.kv_size = num_kv_heads * head_dim
         self.v_size = num_kv_heads * self.value_dim
         self.o_size = num_heads * self.value_dim
-        self.q_norm = build_norm(qk_norm) if qk_norm is not None else None
-        self.k_norm = build_norm(qk_norm) if (qk_norm is not None and self.own_kv) else None
+        if self.whole_norm:
+            from dataclasses import replace
+
+            self.q_norm = build_norm(replace(qk_norm, size=self.q_size))
+            self.k_norm = build_norm(replace(qk_norm, size=self.kv_size))
+        else:
+            self.q_norm = build_norm(qk_norm) if qk_norm is not None else None
+            self.k_norm = build_norm(qk_norm) if (qk_norm is not None and self.own_kv) else None
+        if self.whole_norm and self.value_unit_norm and self.q_norm.eps != self.norm_eps:
+            raise ValueError("the whole-projection norm and the values' unit norm share one eps (qk_norm.eps = norm_eps)")
+        if self.rows_form and not self.whole_norm and qk_norm is not None:
+            raise ValueError("value_unit_norm / head_temperature take the q/k norm over the whole projection or none")
         self.position = build_position_encoding(position) if position is not None else None
-        self.general = bool(self.conv_taps or self.score_cap or self.talking_heads or value_mix
+        if getattr(self.position, "interleaved", False) and not self.rows_form:
+            raise ValueError("a rotation of neighbouring dimensions needs whole_norm, value_unit_norm or head_temperature")
+        self.general = bool(self.conv_taps or self.score_cap or self.talking_heads or value_mix or self.rows_form
                             or self.unit_norm_after_rotation or getattr(self.position, "computed", False))
         if self.general and self.position is not None and not getattr(self.position, "computed", False):
             raise ValueError("these attention options take a position encoding of kind 'rope_computed' (or none)")
@@ -136,6 +171,8 @@ class PagedAttention(Mixer):
             d[n["talk"]] = ParamDecl((self.num_heads, self.num_heads), "bias32")
         if self.value_mix:
             d[n["vmix"]] = ParamDecl((), "bias32")
+        if self.head_temperature:
+            d[n["temp"]] = ParamDecl((self.num_heads,), "norm")
         return d
 
     def subparts(self):
@@ -173,6 +210,8 @@ class PagedAttention(Mixer):
             self.tensors[n["talk"]] = make(n["talk"], ParamDecl((self.num_heads, self.num_heads), "bias32"))
         if self.value_mix:
             self.tensors[n["vmix"]] = make(n["vmix"], ParamDecl((), "bias32"))
+        if self.head_temperature:
+            self.tensors[n["temp"]] = make(n["temp"], ParamDecl((self.num_heads,), "norm"))
         if self.position is not None:
             self.position.build_tables(self.w_qkv.device)
 
@@ -242,6 +281,16 @@ class PagedAttention(Mixer):
         state = cache.state if self.conv_taps > 1 else None
         if self.conv_taps > 1 and state is None:
             raise RuntimeError("the attention's convolution was given no state rows")
+        if self.rows_form:
+            K.qkv_rows_prepare(
+                qkv, q, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, ctx.positions,
+                g.slot_mapping if cache.writes else None, cache.k_pages, cache.v_pages,
+                q_w=self.q_norm.weight if self.whole_norm else None, k_w=self.k_norm.weight if self.whole_norm else None,
+                eps=self.q_norm.eps if self.whole_norm else self.norm_eps, inv_freq=tables.get("inv_freq"),
+                rotary_dim=rotary_dim, interleaved=bool(getattr(self.position, "interleaved", False)),
+                q_head_scale=self.tensors[self.names["temp"]] if self.head_temperature else None,
+                value_unit_norm=self.value_unit_norm)
+            return self._attend(q, x, ctx, cache, project_output)
         K.qkv_prepare(
             qkv, q, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, ctx.positions,
             g.slot_mapping if cache.writes else None, cache.k_pages, cache.v_pages,
@@ -254,10 +303,28 @@ class PagedAttention(Mixer):
             vmix_mode=mode, vmix_lambda=self.tensors[self.names["vmix"]] if mode == 2 else None, v_first=v_first)
         if state is not None:
             K.conv_state_update(qkv, self.conv_taps, state, ctx.cu_q, ctx.token_req, ctx.req_slots, ctx.num_requests)
+        return self._attend(q, x, ctx, cache, project_output)
+
+    def _attend(self, q, x, ctx, cache, project_output: bool):
+        """The prepared queries over the pages, then the mixing of heads (if any) and the output projection."""
+        K = kernels()
+        T = x.shape[0]
+        ws, g = ctx.workspace, cache.group
         attn = ws.tokens("attn.out", T, self.o_size, x.dtype)
         parts = None
         if self.talking_heads:
             parts = ws.tokens("attn.parts", T, self.num_heads * self.num_kv_heads * self.value_dim, torch.float32)
+        if self.rows_form and (self.value_dim != self.head_dim or self.head_dim not in (64, 128)):
+            # head sizes the kernels below take only in their general form: the windowed kernel runs multiples of 16
+            # on the tensor cores (and falls back to the general kernel itself)
+            K.windowed_attention(q, attn, cache.k_pages, cache.v_pages, g.block_table, g.req_slots, ctx.cu_q, g.kv_len,
+                                 ctx.token_req, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim,
+                                 g.page_size, self.window or 0, self.scale, num_requests=ctx.num_requests, workspace=ws)
+            if not project_output:
+                return attn
+            out = ws.tokens("mixer.out", T, self.hidden_size, x.dtype)
+            linear(attn, self.tensors[self.names["o"]], out)
+            return out
         K.paged_attention(
             q, attn, cache.k_pages, cache.v_pages, g.block_table, g.req_slots, ctx.cu_q, g.kv_len, ctx.token_req,
             self.num_heads, self.num_kv_heads, self.head_dim, g.page_size, self.window or 0, self.scale, ctx,

@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import kernels
-from .base import Block, ParamDecl
+from .base import Block, Norm, ParamDecl
 from .linear import linear
 from .registry import build_norm, register_block
 
@@ -425,6 +425,96 @@ class SandwichResidualBlock(Block):
             K.norm_add_norm(stream, f, w, eps, 1.0, center, next_norm=(*nxt, h2) if nxt is not None else None)
         else:
             K.norm_add_norm(stream, a, w, eps, 1.0, center, next_norm=(*nxt, h2) if nxt is not None else None)
+        if nxt is not None:
+            ctx.prepared_norm = (next_norm, h2)
+        ctx.stream_operand = None
+        return None, stream
+
+
+@register_block("prenorm_scaled")
+class PreNormScaledBlock(Block):
+    """A pre-norm layer on a 32-bit residual stream, with an optional scale per channel on each sub-layer's output:
+
+        x <- x + s1 * mixer(norm_1(x));   x <- x + s2 * feed_forward(norm_2(x))
+
+    (`layer_scale` False: s1 = s2 = 1 and no tensors for them.)  A layer may have no feed-forward (then neither its
+    norm nor its scale).  The norms must offer `row_params()`: the kernel that adds a sub-layer's scaled output to the
+    stream also leaves the rows of the norm that reads the stream next (this block's second one, or the next block's
+    first, `ctx.prepared_norm`), so the stream is read and written once per sub-layer.  The sum is 32-bit; the
+    sub-layers' operands are the normed rows rounded to the engine's dtype."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, names=None, layer_scale: bool = False):
+        super().__init__()
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a feed-forward and its norm come together or not at all")
+        for nm in (mixer_norm, feed_forward_norm):
+            if nm is not None and (not hasattr(nm, "row_params") or nm.row_params.__func__ is Norm.row_params):
+                raise ValueError(f"{type(nm).__name__} cannot be folded into the stream's row kernels")
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.layer_scale = bool(layer_scale)
+        self.hidden_size = mixer_norm.size
+        n = dict(mixer="mixer.", feed_forward="feed_forward.", mixer_norm="mixer_norm.",
+                 feed_forward_norm="feed_forward_norm.", mixer_scale="mixer_scale", feed_forward_scale="feed_forward_scale")
+        n.update(names or {})
+        self.names = n
+
+    def subparts(self):
+        n = self.names
+        s = {n["mixer_norm"]: self.mixer_norm, n["mixer"]: self.mixer}
+        if self.feed_forward is not None:
+            s[n["feed_forward_norm"]] = self.feed_forward_norm
+            s[n["feed_forward"]] = self.feed_forward
+        return s
+
+    def param_decls(self):
+        if not self.layer_scale:
+            return {}
+        d = {self.names["mixer_scale"]: ParamDecl((self.hidden_size,), "norm")}
+        if self.feed_forward is not None:
+            d[self.names["feed_forward_scale"]] = ParamDecl((self.hidden_size,), "norm")
+        return d
+
+    def activation_elems(self):
+        ff = self.feed_forward.activation_elems() if self.feed_forward is not None else 0
+        return 3 * self.hidden_size + max(self.mixer.activation_elems(), ff)
+
+    takes_next_norm = True  # `forward` accepts the norm that the next block will apply first
+
+    def accepts_folded_norm(self) -> bool:
+        """True: this block can start from normed rows that whoever updated the stream last left in
+        `ctx.prepared_norm`."""
+        return self.mixer_norm.row_params() is not None
+
+    def forward(self, x, residual, ctx, cache, next_norm=None):
+        """The stream arrives as `x` (first block, residual None) or as `residual` (x None); returns (None, stream)."""
+        K = kernels()
+        stream = residual if residual is not None else x
+        if stream.dtype != torch.float32:
+            raise RuntimeError("this block takes a 32-bit residual stream (ModelSpec.stream_dtype='float32')")
+        T, W = stream.shape
+        ws = ctx.workspace
+        dt = self.mixer.operand_dtype()
+        prepared, ctx.prepared_norm = getattr(ctx, "prepared_norm", None), None
+        if prepared is not None and prepared[0] is self.mixer_norm and prepared[1].shape == (T, W):
+            h = prepared[1]
+        else:
+            h = ws.tokens("block.normed", T, W, dt)
+            self.mixer_norm.forward_rows(stream, None, h)
+        a = self.mixer.forward(h, ctx, cache)
+        nxt = next_norm.row_params() if (next_norm is not None and hasattr(next_norm, "row_params")) else None
+        if nxt is not None and nxt[0].numel() != W:
+            nxt = None
+        # (every reader of h is done when the kernel that overwrites it runs: the rows take its place)
+        h2 = ws.tokens("block.normed", T, W, dt)
+        s1 = self.tensors[self.names["mixer_scale"]] if self.layer_scale else None
+        if self.feed_forward is not None:
+            K.norm_add_norm(stream, a, s1, plain=True, next_norm=(*self.feed_forward_norm.row_params(), h2))
+            f = self.feed_forward.forward(h2, ctx)
+            s2 = self.tensors[self.names["feed_forward_scale"]] if self.layer_scale else None
+            K.norm_add_norm(stream, f, s2, plain=True, next_norm=(*nxt, h2) if nxt is not None else None)
+        else:
+            K.norm_add_norm(stream, a, s1, plain=True, next_norm=(*nxt, h2) if nxt is not None else None)
         if nxt is not None:
             ctx.prepared_norm = (next_norm, h2)
         ctx.stream_operand = None

@@ -43,7 +43,7 @@ class DecoderModel(Part):
         if spec.token_side is not None:
             self.token_side = TokenSideTable(spec.vocab_size, spec.token_side.dim, spec.token_side.shares)
         self.schedule = list(spec.schedule)
-        self._keeps_input = any(e.add_input for e in self.schedule)
+        self._keeps_input = any(e.add_input or e.project_input for e in self.schedule)
         # one mixer of each group answers `graph_key` for all of its kind
         seen: dict = {}
         for e in self.schedule:
@@ -64,10 +64,13 @@ class DecoderModel(Part):
         return s
 
     def param_decls(self):
-        if self.spec.pass_vectors is None:
-            return {}
-        name, rows = self.spec.pass_vectors
-        return {name: ParamDecl((rows, self.spec.hidden_size), "bias32")}
+        d = {}
+        if self.spec.pass_vectors is not None:
+            name, rows = self.spec.pass_vectors
+            d[name] = ParamDecl((rows, self.spec.hidden_size), "bias32")
+        if self.spec.pass_projection is not None:
+            d[self.spec.pass_projection] = ParamDecl((self.spec.hidden_size, 2 * self.spec.hidden_size))
+        return d
 
     # -- what the cache manager needs to know ------------------------------
     def cache_needs(self):
@@ -123,6 +126,8 @@ class DecoderModel(Part):
         n = len(self.schedule)
         for i, e in enumerate(self.schedule):
             block = self.blocks[e.layer]
+            if e.project_input:
+                self._project_stream(residual if residual is not None else x, x0, ctx)
             if e.add_input or e.add_vector is not None:
                 self._add_to_stream(residual if residual is not None else x, x0 if e.add_input else None,
                                     e.add_vector, block, ctx)
@@ -130,7 +135,8 @@ class DecoderModel(Part):
                 # the norm that the next block applies first, if that block can start from what this one prepares
                 # (not when something is added to the stream in between: that addition prepares it then)
                 nxt = self.blocks[self.schedule[i + 1].layer] if i + 1 < n else None
-                if nxt is not None and (self.schedule[i + 1].add_input or self.schedule[i + 1].add_vector is not None):
+                if nxt is not None and (self.schedule[i + 1].add_input or self.schedule[i + 1].add_vector is not None
+                                        or self.schedule[i + 1].project_input):
                     nxt = None
                 nxt_norm = nxt.mixer_norm if (nxt is not None and nxt.accepts_folded_norm()) else None
                 x, residual = block.forward(x, residual, ctx, caches[i], next_norm=nxt_norm)
@@ -139,6 +145,20 @@ class DecoderModel(Part):
         ctx.folded_norm = None
         ctx.prepared_norm = None
         return x, residual
+
+    def _project_stream(self, stream, x0, ctx) -> None:
+        """stream <- P [stream | x0] with the model's pass projection P [hidden, 2 hidden]: the two 32-bit row sets
+        side by side, rounded to the engine's dtype, are one product's operand; its 32-bit result is the new
+        stream."""
+        if stream is None or stream.dtype != torch.float32 or x0 is None:
+            raise RuntimeError("a projection of the stream between layers needs a 32-bit stream and the kept input")
+        T, H = stream.shape
+        K = kernels()
+        both = ctx.workspace.tokens("model.pass_in", T, 2 * H, self.dtype)
+        K.concat_rows_f32(stream, x0, both)
+        K.linear_f32_out(both, self.tensors[self.spec.pass_projection], stream)
+        ctx.prepared_norm = None
+        ctx.stream_operand = None
 
     def _add_to_stream(self, stream, rows, vector, block, ctx) -> None:
         """stream += rows (if given) + row `vector` of the pass vectors (if given), in this order, in 32-bit; the

@@ -15,7 +15,8 @@ projection).  Options, each a constructor argument:
 * `gated`: the concatenated heads are multiplied by sigmoid(W_g h) in front of the output projection.
 
 `latent_attention`: queries and keys / values through low-rank latents, run in the absorbed form.  With
-c_q = RMSnorm(W_dq h), q = W_uq c_q laid out per head as [dim unrotated | rot rotated], W_dkv h = [kv_rank | rot]
+c_q = RMSnorm(W_dq h), q = W_uq c_q (or, without a query latent, q = W_q h) laid out per head as
+[dim unrotated | rot rotated], W_dkv h = [kv_rank | rot]
 whose first part, RMS-normed, is the latent c and whose second part is ONE rotated key part shared by all heads,
 per head k = [W_uk c | k_rot], v = W_uv c:
 
@@ -23,8 +24,9 @@ per head k = [W_uk c | k_rot], v = W_uv c:
 
 so the cache holds one row [c | k_rot] per token (a single kv head), the query of head h becomes
 [W_uk,h^T q_plain,h | q_rot,h], the values are the first kv_rank elements of the key rows, and the head's output
-in latent space is taken through W_uv,h afterwards.  Rotation: neighbours (2i, 2i + 1) of the first `dims`
-rotated dimensions turn by position * theta^(-2i / dims), angles in 32-bit.
+in latent space is taken through W_uv,h afterwards.  Rotation: neighbours (2i, 2i + 1), or the halves (i, i + dims / 2),
+of the first `dims` rotated dimensions turn by position * theta^(-2i / dims), angles in 32-bit.  `gated`: the
+concatenated heads (after W_uv) are multiplied by sigmoid(W_g h) in front of the output projection.
 """
 
 from __future__ import annotations
@@ -172,15 +174,16 @@ class KVSharedAttention(Mixer, _ProjectsOutput):
 
 @register_mixer("latent_attention")
 class LatentAttention(Mixer):
-    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, value_dim: int, q_rank: int,
-                 kv_rank: int, position, scale: float | None = None, window: int | None = None, pool: int = 0,
-                 norm_eps: float = 1e-6, names: dict | None = None):
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, value_dim: int,
+                 q_rank: int | None, kv_rank: int, position, scale: float | None = None, window: int | None = None,
+                 pool: int = 0, norm_eps: float = 1e-6, names: dict | None = None, gated: bool = False):
         """`head_dim`: the unrotated query / key size per head, `rot_dim` the rotated one; `position`: a
-        `PositionSpec` of kind `rope_computed` with `interleaved=True` (its `rotary_dim` <= `rot_dim` dimensions
-        turn, the rest pass).  `window`, `pool`: as for `kv_shared_attention` (a pooled block's key row is the
-        mean of the cached rows [c | k_rot], its value the mean latent)."""
+        `PositionSpec` of kind `rope_computed`, with `interleaved` or not (its `rotary_dim` <= `rot_dim` dimensions
+        turn, the rest pass).  `q_rank` None: no query latent, one projection `q` gives the queries.  `window`,
+        `pool`: as for `kv_shared_attention` (a pooled block's key row is the mean of the cached rows [c | k_rot],
+        its value the mean latent).  `gated`: a sigmoid output gate `g` [heads * value_dim, hidden]."""
         super().__init__()
-        if min(hidden_size, num_heads, head_dim, value_dim, q_rank, kv_rank) <= 0 or rot_dim < 0:
+        if min(hidden_size, num_heads, head_dim, value_dim, kv_rank) <= 0 or rot_dim < 0 or (q_rank is not None and q_rank <= 0):
             raise ValueError("sizes must be positive")
         if kv_rank + rot_dim > 640 or kv_rank > 512:
             raise ValueError(f"kv_rank {kv_rank} + rot_dim {rot_dim}: the attention kernels take key rows up to 640 "
@@ -191,35 +194,42 @@ class LatentAttention(Mixer):
             raise ValueError("pooled blocks lie behind a window: pool needs one")
         self.hidden_size, self.num_heads, self.head_dim, self.rot_dim = hidden_size, num_heads, head_dim, rot_dim
         self.value_dim, self.q_rank, self.kv_rank = value_dim, q_rank, kv_rank
+        self.gated = bool(gated)
         self.scale = (head_dim + rot_dim) ** -0.5 if scale is None else float(scale)
         self.window, self.pool, self.norm_eps = window, int(pool), float(norm_eps)
         self.position = build_position_encoding(position) if (position is not None and rot_dim) else None
         if self.position is not None:
-            if not getattr(self.position, "computed", False) or not getattr(self.position, "interleaved", False):
-                raise ValueError("latent attention takes a position encoding of kind 'rope_computed' with "
-                                 "interleaved=True")
+            if not getattr(self.position, "computed", False):
+                raise ValueError("latent attention takes a position encoding of kind 'rope_computed'")
             if self.position.rotary_dim > rot_dim:
                 raise ValueError("more rotated dimensions than the rotated part has")
-        n = dict(dq="q_a_proj.weight", dq_norm="q_a_norm", uq="q_b_proj.weight", dkv="kv_a_proj.weight",
-                 dkv_norm="kv_a_norm", uk="k_b_proj.weight", uv="v_b_proj.weight", o="o_proj.weight")
+        n = dict(dq="q_a_proj.weight", dq_norm="q_a_norm", uq="q_b_proj.weight", q="q_proj.weight", dkv="kv_a_proj.weight",
+                 dkv_norm="kv_a_norm", uk="k_b_proj.weight", uv="v_b_proj.weight", g="g_proj.weight", o="o_proj.weight")
         n.update(names or {})
         self.names = n
         self.key_row = kv_rank + rot_dim
 
     def param_decls(self):
         H, n, N = self.hidden_size, self.names, self.num_heads
-        return {
-            n["dq"]: ParamDecl((self.q_rank, H)), n["dq_norm"]: ParamDecl((self.q_rank,), "norm"),
-            n["uq"]: ParamDecl((N * (self.head_dim + self.rot_dim), self.q_rank)),
+        d = {
             n["dkv"]: ParamDecl((self.key_row, H)), n["dkv_norm"]: ParamDecl((self.kv_rank,), "norm"),
             n["uk"]: ParamDecl((N * self.head_dim, self.kv_rank)), n["uv"]: ParamDecl((N * self.value_dim, self.kv_rank)),
             n["o"]: ParamDecl((H, N * self.value_dim)),
         }
+        if self.q_rank is None:
+            d[n["q"]] = ParamDecl((N * (self.head_dim + self.rot_dim), H))
+        else:
+            d[n["dq"]] = ParamDecl((self.q_rank, H))
+            d[n["dq_norm"]] = ParamDecl((self.q_rank,), "norm")
+            d[n["uq"]] = ParamDecl((N * (self.head_dim + self.rot_dim), self.q_rank))
+        if self.gated:
+            d[n["g"]] = ParamDecl((N * self.value_dim, H))
+        return d
 
     def materialize(self, make):
         super().materialize(make)
         if self.position is not None:
-            self.position.build_tables(self.tensors[self.names["dq"]].device)
+            self.position.build_tables(self.tensors[self.names["dkv"]].device)
 
     def cache_need(self):
         window = None if self.window is None else max(self.window, self.pool)
@@ -230,8 +240,8 @@ class LatentAttention(Mixer):
 
     def activation_elems(self):
         N = self.num_heads
-        return (self.q_rank + self.key_row + N * (self.head_dim + self.rot_dim) + N * self.kv_rank + N * self.key_row
-                + N * self.kv_rank + N * self.value_dim + self.hidden_size)
+        return ((self.q_rank or 0) + self.key_row + N * (self.head_dim + self.rot_dim) + N * self.kv_rank
+                + N * self.key_row + N * self.kv_rank + (2 if self.gated else 1) * N * self.value_dim + self.hidden_size)
 
     def graph_key_group(self):
         return (type(self), self.num_heads, self.key_row, self.pool)
@@ -247,11 +257,14 @@ class LatentAttention(Mixer):
         if g is None or not cache.writes:
             raise RuntimeError("latent attention keeps a cache of its own: it was given none to write")
         dt = x.dtype
-        cq = ws.tokens("lat.cq", T, self.q_rank, dt)
-        linear(x, self.tensors[n["dq"]], cq)
-        K.add_rmsnorm(cq, None, self.tensors[n["dq_norm"]], self.norm_eps, cq)
         q_full = ws.tokens("lat.q", T, N * (d + r), dt)
-        linear(cq, self.tensors[n["uq"]], q_full)
+        if self.q_rank is None:
+            linear(x, self.tensors[n["q"]], q_full)
+        else:
+            cq = ws.tokens("lat.cq", T, self.q_rank, dt)
+            linear(x, self.tensors[n["dq"]], cq)
+            K.add_rmsnorm(cq, None, self.tensors[n["dq_norm"]], self.norm_eps, cq)
+            linear(cq, self.tensors[n["uq"]], q_full)
         dkv = ws.tokens("lat.dkv", T, self.key_row, dt)
         linear(x, self.tensors[n["dkv"]], dkv)
         # every head's unrotated query through its key up-projection: [heads, T, dim] x [heads, dim, rank]
@@ -261,7 +274,7 @@ class LatentAttention(Mixer):
         tables = self.position.tables() if self.position is not None else {}
         K.latent_prepare(q_full, q_lat, dkv, q_out, N, d, r, R, self.position.rotary_dim if self.position else 0,
                          self.tensors[n["dkv_norm"]], self.norm_eps, tables.get("inv_freq"), ctx.positions,
-                         g.slot_mapping, cache.k_pages)
+                         g.slot_mapping, cache.k_pages, interleaved=bool(getattr(self.position, "interleaved", True)))
         pooled = None
         if self.pool:
             aux = cache.aux
@@ -278,6 +291,10 @@ class LatentAttention(Mixer):
         attn = ws.tokens("attn.out", T, N * dv, dt)
         batched_matmul(o_lat.view(T, N, R).transpose(0, 1), self.tensors[n["uv"]].view(N, dv, R).transpose(1, 2),
                        attn.view(T, N, dv).transpose(0, 1))
+        if self.gated:
+            gate = ws.tokens("lat.gate", T, N * dv, dt)
+            linear(x, self.tensors[n["g"]], gate)
+            K.sigmoid_gate(attn, gate)
         out = ws.tokens("mixer.out", T, self.hidden_size, dt)
         linear(attn, self.tensors[n["o"]], out)
         return out
