@@ -372,10 +372,14 @@ class CpuKernels:
         x = (x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps)).reshape(T, -1)
         out.copy_((x * weight * torch.sigmoid(g.float())).to(out.dtype))
 
-    def moe_route(self, logits, choice, weight, top, softmax_scores=False, renormalize=False):
+    def moe_route(self, logits, choice, weight, top, softmax_scores=False, renormalize=False, correction=None,
+                  experts=None):
         self._count("moe")
+        if experts is not None:
+            logits = logits[:, :experts]
         s = torch.softmax(logits, -1) if softmax_scores else torch.sigmoid(logits)
-        w, c = torch.topk(s, top, dim=-1)
+        c = torch.topk(s if correction is None else s + correction, top, dim=-1).indices
+        w = torch.gather(s, 1, c)
         if renormalize:
             w = w / w.sum(-1, keepdim=True)
         choice.copy_(c.to(torch.int32))
@@ -383,14 +387,15 @@ class CpuKernels:
 
     def moe_arrange(self, choice, pairs, experts, offsets, sorted_pairs, place):
         c = choice.reshape(-1)[:pairs].long()
-        order = torch.argsort(c, stable=True)
+        order = torch.argsort(c, stable=True)  # (choices at or beyond `experts` come last and get no expert's rows)
         sorted_pairs.view(-1)[:pairs] = order.to(torch.int32)
         place.view(-1)[order] = torch.arange(pairs, dtype=torch.int32)
-        counts = torch.bincount(c, minlength=experts)
+        counts = torch.bincount(c[c < experts], minlength=experts)
         offsets.view(-1)[0] = 0
         offsets.view(-1)[1:experts + 1] = torch.cumsum(counts, 0).to(torch.int32)
 
-    def moe_grouped_linear(self, x, weights, offsets, sorted_pairs, pair_weight, out, top, rows_from_pairs, gated, act=0):
+    def moe_grouped_linear(self, x, weights, offsets, sorted_pairs, pair_weight, out, top, rows_from_pairs, gated, act=0,
+                           limit=0.0, alpha=1.0):
         self._count("moe")
         off = offsets.view(-1).tolist()
         sp = sorted_pairs.view(-1)
@@ -405,16 +410,28 @@ class CpuKernels:
                     y = y * pw[pair]
                 if gated:
                     g, u = y[:n_out], y[n_out:]
-                    y = (g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")) * u
+                    if act == 2:
+                        g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+                        y = g * torch.sigmoid(alpha * g) * (u + 1)
+                    else:
+                        y = (g * torch.sigmoid(g) if act == 0 else torch.nn.functional.gelu(g, approximate="tanh")) * u
                 out[p] = y.to(out.dtype)
 
-    def moe_combine(self, rows, place, pair_weight, y, top):
+    def moe_combine(self, rows, place, pair_weight, y, top, passing=None, shared=None):
         T = y.shape[0]
         pl = place.view(-1)[: T * top].long()
-        v = rows[pl].float()
+        v = rows[pl.clamp(0, rows.shape[0] - 1)].float()
+        if passing is not None:
+            choice, experts, x = passing
+            passes = choice.view(-1)[: T * top] >= experts
+            v = torch.where(passes[:, None], x.float().repeat_interleave(top, 0), v)
         if pair_weight is not None:
             v = v * pair_weight.view(-1)[: T * top, None]
-        y.copy_(v.view(T, top, -1).sum(1).to(y.dtype))
+        out = v.view(T, top, -1).sum(1)
+        if shared is not None:
+            s_rows, gate = shared
+            out = out + s_rows.float() * (torch.sigmoid(gate[:, :1]) if gate is not None else 1.0)
+        y.copy_(out.to(y.dtype))
 
     def argmax(self, logits, out):
         out[: logits.shape[0]] = torch.argmax(logits, -1).to(torch.int32)
