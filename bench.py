@@ -788,6 +788,66 @@ def run_pidenex(args) -> dict:
     return out
 
 
+# ---------------------------------------------------------------------------------------------------------
+# `--workload finosun`: the Finosun decoder beside the Ludalix decoder with windowed attention and routed experts in
+# every layer (the closest design the engine has: grouped windowed attention and routed experts on a 32-bit stream)
+# ---------------------------------------------------------------------------------------------------------
+FINOSUN_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, window=1024, experts=16, top=2, expert_ff=1024, shared_ff=2048,
+                  kv_rank=384, vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, window=2048, experts=32, top=2, expert_ff=2048, shared_ff=4096,
+                  kv_rank=384, vocab=32768),
+}
+
+
+def finosun_config(width: int, heads: int, kv_heads: int, window: int, experts: int, top: int, expert_ff: int,
+                   shared_ff: int, kv_rank: int, vocab: int) -> dict:
+    """Eight layer runs: a windowed layer and a latent layer that run three times, then one more of each; every one
+    with routed experts (two of them passing ones) and a gated shared expert."""
+    att = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5, mask=dict(size=window),
+               rot=dict(dims=64, base=1e6))
+    lat = dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=kv_rank, scale=192 ** -0.5, rot=dict(dims=64, base=1e6))
+    mlp = dict(kind="moe", expert=dict(ff=expert_ff, limit=7.0), router=dict(experts=experts, identity=2, top=top),
+               shared=dict(ff=shared_ff, limit=7.0))
+    kinds = [("attention", att), ("latent_attention", lat)]
+    layers = [dict(type=t, mixer=dict(m), mlp=dict(mlp)) for _ in range(2) for t, m in kinds]
+    return dict(architecture="Finosun", vocab=vocab, width=width, norm=dict(eps=1e-5), layers=layers,
+                loop=dict(start=0, stop=2, times=3), torch_dtype="bfloat16")
+
+
+def ludalix_routed_config(width: int, heads: int, kv_heads: int, window: int, experts: int, top: int, expert_ff: int,
+                          shared_ff: int, kv_rank: int, vocab: int) -> dict:
+    """Eight layers of windowed attention (no kept tokens) with routed experts of the same sizes."""
+    att = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, mask=dict(size=window, keep_first=0), scale=128 ** -0.5)
+    moe = dict(kind="moe", expert=dict(ff=expert_ff), router=dict(experts=experts, top=top))
+    layers = [dict(type="attention", mixer=dict(att), mlp=dict(moe)) for _ in range(8)]
+    return dict(architecture="Ludalix", vocab=vocab, width=width, residual_mult=0.5, embedding=dict(scale=12.0),
+                norm=dict(eps=1e-6), layers=layers, torch_dtype="bfloat16")
+
+
+def run_finosun(args) -> dict:
+    """`--workload finosun`: prefill (one prompt of 2,048 tokens) and decode (8 requests holding 2,048 tokens each)
+    of the Finosun decoder at layer sizes that resemble a real model's, random weights, beside the Ludalix decoder
+    with windowed attention and routed experts of equal sizes in as many layers as the Finosun model has layer
+    runs; per kernel group the device time of one eager step of each kind.  One JSON object; the default workload
+    and its line are untouched."""
+    T, B, ctx_len = PREFILL_TOKENS, args.batch, START_CONTEXT
+    out = {"workload": "finosun", "prefill_tokens": T, "decode_batch": B, "decode_context": ctx_len,
+           "data": "synthetic", "dtype": "bf16", "peaks": peaks(), "sizes": {}}
+    names = [args.case] if args.case else list(FINOSUN_SIZES)
+    for name in names:
+        size = FINOSUN_SIZES[name]
+        out["sizes"][name] = {}
+        fin = finosun_config(**size)
+        runs = len(fin["layers"]) + (fin["loop"]["times"] - 1) * (fin["loop"]["stop"] - fin["loop"]["start"])
+        for label, cfg, n in (("finosun", fin, runs), ("ludalix_routed", ludalix_routed_config(**size), 8)):
+            if args.only_model and args.only_model != label:
+                continue
+            out["sizes"][name][label] = dict(_measure_model(cfg, False, T, B, ctx_len, args.steps, args.warmup),
+                                             layer_runs=n)
+    return out
+
+
 def run_extra_shapes(args, impl: str) -> dict:
     """The two further workloads, each in a process of its own (the 32B shape needs the device to itself), as
     flat entries for `points`."""
@@ -1450,7 +1510,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--workload", default="8b", choices=["8b", "32b", "serve-0.6b", "8b-long", "ludalix", "borosun", "pidenex"],
+    ap.add_argument("--workload", default="8b", choices=["8b", "32b", "serve-0.6b", "8b-long", "ludalix", "borosun", "pidenex", "finosun"],
                     help="8b: the default line (Qwen3-8B layer sizes); 32b: the same at Qwen3-32B layer sizes; "
                          "serve-0.6b: 256 requests under continuous batching at Qwen3-0.6B layer sizes; 8b-long: "
                          "prefill of 16,384 tokens and decode of 8 requests at that context")
@@ -1464,7 +1524,7 @@ def main() -> int:
                     help="--probe linear: launch only this kernel, eagerly, --steps times (for a profiler)")
     ap.add_argument("--shape", default="gate_up", choices=["qkv", "o", "gate_up", "down", "head"],
                     help="--probe linear --only: which of the decode step's products")
-    ap.add_argument("--only-model", default=None, help="--workload borosun / pidenex: measure only this model (borosun or pidenex, ludalix_dense)")
+    ap.add_argument("--only-model", default=None, help="--workload borosun / pidenex / finosun: measure only this model (borosun, pidenex or finosun; ludalix_dense, ludalix_routed)")
     ap.add_argument("--case", default=None, help="run only the case of this name (--probe prefill-attention, decode-attention)")
     ap.add_argument("--context", type=int, default=START_CONTEXT, help="tokens each request holds (--probe)")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens of a page (--probe decode-attention)")
@@ -1509,6 +1569,9 @@ def main() -> int:
         return 0
     if args.workload == "pidenex":
         print(json.dumps(run_pidenex(args)))
+        return 0
+    if args.workload == "finosun":
+        print(json.dumps(run_finosun(args)))
         return 0
     out = run_serve(args) if args.workload == "serve-0.6b" else run_ours(args)
     if extra:
