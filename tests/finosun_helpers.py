@@ -64,12 +64,13 @@ CFG_C = config(100, 130, [
 ])
 # D: values the other three make equal or leave out: a loop of one pass over one layer, one head, a window of one,
 # attention without rotation and without a window, a latent without a rotated part, one expert, only passing
-# experts beside it
+# experts beside it, heads of an odd size
 CFG_D = config(48, 61, [
     ("attention", attention(1, 1, 32, 32, 0.2, 1, rot_dims=2), moe(1, 0, 1, 32, 1.0)),
     ("latent_attention", latent(1, 24, 0, 16, 24, 0.2), None),
     ("attention", attention(3, 3, 16, 24, 0.25, None), moe(1, 3, 2, 24, 1.1, shared=(8, 1.0))),
     ("latent_attention", latent(2, 8, 8, 8, 8, 0.3, base=3.0), moe(2, 0, 2, 16, 0.9)),
+    ("attention", attention(2, 1, 15, 9, 0.25, 6, rot_dims=6, base=11.0), None),
 ], loop=(2, 3, 1))
 # E: sizes the tensor-core attention kernels of the 16-bit path take: grouped heads of 64 and 128 with windows
 # longer than a key tile, heads of 32 with values of 48, a latent whose key row (112 + 16) is a multiple of 16 and

@@ -41,7 +41,7 @@ def test_a_loop_unrolls_into_runs_with_the_projection_at_the_first_layer_of_each
         assert (spec.pass_projection == "loop.in") == ("loop" in cfg)
     assert len(_spec(CFG_A).schedule) == 1 + 2 * 2 and len(_spec(CFG_B).schedule) == 6
     assert [s for _, s in pf.layer_runs(CFG_B)] == [True, False] * 3  # the first pass starts with it too
-    assert [s for _, s in pf.layer_runs(CFG_D)] == [False, False, True, False]
+    assert [s for _, s in pf.layer_runs(CFG_D)] == [False, False, True, False, False]
 
 
 def test_allocated_tensors_have_the_declared_names_and_32_bit_where_the_arithmetic_is():

@@ -298,6 +298,133 @@ __global__ void qkv_rows_prepare_kernel(const T* __restrict__ qkv, long long str
   }
 }
 
+// The same work with the token's row staged once in shared memory as 32-bit values (16-byte loads where the rows
+// allow), the sums of squares formed while it is staged, and q and k handled two neighbouring channels at a time
+// (a rotation of neighbours then needs no second read; paired stores).  Needs an even head size; `row` holds
+// q | k | v.
+template <typename T>
+__global__ void qkv_rows_prepare_staged_kernel(const T* __restrict__ qkv, long long stride, T* __restrict__ q_out,
+                                               int num_q, int num_kv, int head_dim, int v_dim,
+                                               const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                                               const float* __restrict__ inv_freq, int rot_dims, int interleaved,
+                                               const int* __restrict__ positions,
+                                               const float* __restrict__ q_head_scale, int v_unit,
+                                               const int* __restrict__ slot_mapping, T* __restrict__ k_pages,
+                                               T* __restrict__ v_pages, long long num_slots, int wide, int* status) {
+  extern __shared__ float prep_row[];
+  __shared__ float scratch[33];
+  __shared__ float cs_s[ROWS_MAX_ROT / 2], sn_s[ROWS_MAX_ROT / 2];
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const int t = blockIdx.x;
+  const int q_size = num_q * head_dim, k_size = num_kv * head_dim, v_size = num_kv * v_dim;
+  const int width = q_size + k_size + v_size;
+  const T* src = qkv + (long long)t * stride;
+  long long slot = slot_mapping != nullptr ? slot_mapping[t] : -1;
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) ullm_report(status, ULLM_STATUS_SLOT, t, (int)slot);
+    slot = -1;
+  }
+  const int half = rot_dims >> 1;
+  if (rot_dims > 0) {
+    const float p = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(p * inv_freq[i], &sn_s[i], &cs_s[i]);
+  }
+  float acc_q = 0.f, acc_k = 0.f;
+  if (wide) {  // (q_size and k_size are multiples of VEC: a piece lies in one of the three parts)
+    for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + c);
+      const T* e = reinterpret_cast<const T*>(&raw);
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const float x = to_f32(e[i]);
+        prep_row[c + i] = x;
+        sq += x * x;
+      }
+      if (c < q_size) acc_q += sq;
+      else if (c < q_size + k_size) acc_k += sq;
+    }
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      const float x = to_f32(src[c]);
+      prep_row[c] = x;
+      if (c < q_size) acc_q += x * x;
+      else if (c < q_size + k_size) acc_k += x * x;
+    }
+  }
+  float rq = 1.f, rk = 1.f;
+  if (wq != nullptr) {
+    rq = 1.f / sqrtf(block_sum(acc_q, scratch) / (float)q_size + eps);
+    rk = 1.f / sqrtf(block_sum(acc_k, scratch) / (float)k_size + eps);
+  } else {
+    __syncthreads();
+  }
+  // q and k, two neighbouring channels per thread
+  for (int c = threadIdx.x * 2; c < q_size + k_size; c += blockDim.x * 2) {
+    const bool is_q = c < q_size;
+    const int cc = is_q ? c : c - q_size;
+    const float* w = is_q ? wq : wk;
+    const float r = is_q ? rq : rk;
+    const int h = cc / head_dim, j = cc - h * head_dim;  // (j is even, j + 1 in the same head)
+    float x0 = prep_row[c] * r, x1 = prep_row[c + 1] * r;
+    if (w != nullptr) {
+      x0 *= w[cc];
+      x1 *= w[cc + 1];
+    }
+    if (j < rot_dims) {
+      if (interleaved) {
+        const float cs = cs_s[j >> 1], sn = sn_s[j >> 1];
+        const float a = x0 * cs - x1 * sn, b = x1 * cs + x0 * sn;
+        x0 = a;
+        x1 = b;
+      } else {
+        // (rot_dims / 2 may be odd: the two channels are looked at one by one)
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int ji = j + i;
+          if (ji >= rot_dims) continue;
+          const bool second = ji >= half;
+          const int pj = second ? ji - half : ji + half, fi = second ? ji - half : ji;
+          const int pc = c - j + pj;
+          float other = prep_row[pc] * r;
+          if (w != nullptr) other *= w[cc - j + pj];
+          float& x = i ? x1 : x0;
+          x = second ? x * cs_s[fi] + other * sn_s[fi] : x * cs_s[fi] - other * sn_s[fi];
+        }
+      }
+    }
+    if (is_q) {
+      if (q_head_scale != nullptr) {
+        x0 *= q_head_scale[h];
+        x1 *= q_head_scale[h];
+      }
+      T* dst = q_out + (long long)t * q_size + cc;
+      dst[0] = from_f32<T>(x0);
+      dst[1] = from_f32<T>(x1);
+    } else if (slot >= 0) {
+      T* dst = k_pages + slot * k_size + cc;
+      dst[0] = from_f32<T>(x0);
+      dst[1] = from_f32<T>(x1);
+    }
+  }
+  if (slot < 0) return;
+  // v: a warp per value head
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const float* v = prep_row + q_size + k_size;
+  for (int g = warp; g < num_kv; g += warps) {
+    const float* vs = v + g * v_dim;
+    float r = 1.f;
+    if (v_unit) {
+      float acc = 0.f;
+      for (int j = lane; j < v_dim; j += 32) acc += vs[j] * vs[j];
+      r = 1.f / sqrtf(warp_sum(acc) / (float)v_dim + eps);
+    }
+    for (int j = lane; j < v_dim; j += 32) v_pages[slot * v_size + g * v_dim + j] = from_f32<T>(vs[j] * r);
+  }
+}
+
 static inline int prep_threads(int cols) {
   int threads = 32;
   while (threads < 256 && threads * 2 < cols) threads <<= 1;
@@ -381,6 +508,31 @@ extern "C" int ullm_qkv_rows_prepare(int dtype, const void* qkv, long long strid
   if (rot_dims > ROWS_MAX_ROT) return ULLM_ERR_UNSUPPORTED;
   if (tokens == 0) return ULLM_OK;
   const dim3 grid(tokens), block(prep_threads(num_q * head_dim / 4));
+  const long long width = (long long)num_q * head_dim + (long long)num_kv * (head_dim + v_dim);
+  const size_t smem = (size_t)width * sizeof(float);
+  if (head_dim % 2 == 0 && smem <= 160 * 1024) {
+    // the staged form: the row waits in shared memory
+    const int esize = dtype == ULLM_DTYPE_F32 ? 4 : 2, vec = 16 / esize;
+    const int wide = ((uintptr_t)qkv % 16 == 0) && stride % vec == 0 && (num_q * head_dim) % vec == 0 &&
+                     (num_kv * head_dim) % vec == 0 && width % vec == 0;
+#define QRS_GO(T)                                                                                                    \
+  {                                                                                                                  \
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(qkv_rows_prepare_staged_kernel<T>,                                  \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { \
+      cudaGetLastError();                                                                                            \
+      return ULLM_ERR_LAUNCH;                                                                                        \
+    }                                                                                                                \
+    return ullm_launch_kernel(qkv_rows_prepare_staged_kernel<T>, grid, block, smem, st, (const T*)qkv, stride,       \
+                              (T*)q_out, num_q, num_kv, head_dim, v_dim, wq, wk, eps, inv_freq, rot_dims,            \
+                              interleaved, positions, q_head_scale, v_unit, slot_mapping, (T*)k_pages, (T*)v_pages,  \
+                              num_slots, wide, status);                                                              \
+  }
+    if (dtype == ULLM_DTYPE_F32) QRS_GO(float);
+    if (dtype == ULLM_DTYPE_BF16) QRS_GO(__nv_bfloat16);
+    if (dtype == ULLM_DTYPE_F16) QRS_GO(__half);
+#undef QRS_GO
+    return ULLM_ERR_BAD_DTYPE;
+  }
 #define QRP_GO(T)                                                                                                    \
   return ullm_launch_kernel(qkv_rows_prepare_kernel<T>, grid, block, 0, st, (const T*)qkv, stride, (T*)q_out, num_q,  \
                             num_kv, head_dim, v_dim, wq, wk, eps, inv_freq, rot_dims, interleaved, positions,         \

@@ -382,7 +382,22 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
   }
 }
 
-template <typename T>
+// VEC elements of T from p to 32-bit: one 16-byte load when VEC elements are 16 bytes, else element by element.
+template <typename T, int VEC>
+__device__ __forceinline__ void moe_load_vec(const T* __restrict__ p, float (&out)[VEC]) {
+  if constexpr (VEC * sizeof(T) == 16) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) out[i] = to_f32(e[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) out[i] = to_f32(p[i]);
+  }
+}
+
+// A block: one token x (blockDim.x * VEC) columns (blockIdx.y counts the column ranges); a thread: VEC columns.
+template <typename T, int VEC>
 __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __restrict__ place,
                                    const float* __restrict__ pair_weight, T* __restrict__ y, int top, int cols,
                                    const int* __restrict__ choice, int experts, const T* __restrict__ x,
@@ -391,18 +406,35 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __rest
   pdl_launch_dependents();
   pdl_wait();
   const long long t = blockIdx.x;
-  float sg = 1.f;
-  if (shared_rows != nullptr && shared_gate != nullptr) sg = 1.f / (1.f + expf(-shared_gate[t * gate_stride]));
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    float s = 0.f;
-    for (int k = 0; k < top; ++k) {
-      const long long pair = t * top + k;
-      const bool passes = choice != nullptr && choice[pair] >= experts;  // an expert that is its input
-      const float v = passes ? to_f32(x[t * x_stride + c]) : to_f32(rows[(long long)place[pair] * cols + c]);
-      s += pair_weight != nullptr ? pair_weight[pair] * v : v;
-    }
-    if (shared_rows != nullptr) s += sg * to_f32(shared_rows[t * cols + c]);
-    y[t * cols + c] = from_f32<T>(s);
+  const int c0 = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+  if (c0 >= cols) return;
+  float acc[VEC], v[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+  for (int k = 0; k < top; ++k) {
+    const long long pair = t * top + k;
+    const bool passes = choice != nullptr && choice[pair] >= experts;  // an expert that is its input
+    const T* src = passes ? x + t * x_stride : rows + (long long)place[pair] * cols;
+    moe_load_vec<T, VEC>(src + c0, v);
+    const float w = pair_weight != nullptr ? pair_weight[pair] : 1.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] += w * v[i];
+  }
+  if (shared_rows != nullptr) {
+    const float sg = shared_gate != nullptr ? 1.f / (1.f + expf(-shared_gate[t * gate_stride])) : 1.f;
+    moe_load_vec<T, VEC>(shared_rows + t * cols + c0, v);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] += sg * v[i];
+  }
+  if constexpr (VEC * sizeof(T) == 16) {
+    uint4 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) e[i] = from_f32<T>(acc[i]);
+    *reinterpret_cast<uint4*>(y + t * cols + c0) = raw;
+  } else {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) y[t * cols + c0 + i] = from_f32<T>(acc[i]);
   }
 }
 
@@ -508,21 +540,30 @@ extern "C" int ullm_moe_combine(int dtype, const void* rows, const int* place, c
   if (tokens < 0 || top <= 0 || cols <= 0) return ULLM_ERR_BAD_SIZE;
   if (choice != nullptr && (x == nullptr || x_stride < cols || experts < 0)) return ULLM_ERR_BAD_SIZE;
   if (tokens == 0) return ULLM_OK;
+  const int esize = dtype == ULLM_DTYPE_F32 ? 4 : 2;
+  const int vec = 16 / esize;
+  const bool wide = cols % vec == 0 && x_stride % vec == 0 &&
+                    (((uintptr_t)rows | (uintptr_t)y | (uintptr_t)x | (uintptr_t)shared_rows) & 15) == 0;
+  const int per_thread = wide ? vec : 1;
   int threads = 32;
-  while (threads < 256 && threads * 4 < cols) threads <<= 1;
-  const dim3 grid(tokens), block(threads);
-  if (dtype == ULLM_DTYPE_F32)
-    return ullm_launch_kernel(moe_combine_kernel<float>, grid, block, 0, st, (const float*)rows, place, pair_weight,
-                              (float*)y, top, cols, choice, experts, (const float*)x, x_stride,
-                              (const float*)shared_rows, shared_gate, gate_stride);
-  if (dtype == ULLM_DTYPE_BF16)
-    return ullm_launch_kernel(moe_combine_kernel<__nv_bfloat16>, grid, block, 0, st, (const __nv_bfloat16*)rows,
-                              place, pair_weight, (__nv_bfloat16*)y, top, cols, choice, experts,
-                              (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)shared_rows, shared_gate,
-                              gate_stride);
-  if (dtype == ULLM_DTYPE_F16)
-    return ullm_launch_kernel(moe_combine_kernel<__half>, grid, block, 0, st, (const __half*)rows, place, pair_weight,
-                              (__half*)y, top, cols, choice, experts, (const __half*)x, x_stride,
-                              (const __half*)shared_rows, shared_gate, gate_stride);
+  while (threads < 128 && threads * per_thread < cols) threads <<= 1;
+  const dim3 grid(tokens, (cols + threads * per_thread - 1) / (threads * per_thread)), block(threads);
+#define MC_GO(T, V)                                                                                                 \
+  return ullm_launch_kernel(moe_combine_kernel<T, V>, grid, block, 0, st, (const T*)rows, place, pair_weight, (T*)y, \
+                            top, cols, choice, experts, (const T*)x, x_stride, (const T*)shared_rows, shared_gate,  \
+                            gate_stride)
+  if (dtype == ULLM_DTYPE_F32) {
+    if (wide) MC_GO(float, 4);
+    MC_GO(float, 1);
+  }
+  if (dtype == ULLM_DTYPE_BF16) {
+    if (wide) MC_GO(__nv_bfloat16, 8);
+    MC_GO(__nv_bfloat16, 1);
+  }
+  if (dtype == ULLM_DTYPE_F16) {
+    if (wide) MC_GO(__half, 8);
+    MC_GO(__half, 1);
+  }
+#undef MC_GO
   return ULLM_ERR_BAD_DTYPE;
 }

@@ -82,11 +82,15 @@ class RoutedExperts(FeedForward):
 
     def materialize(self, make):
         n, E, I, H = self.names, self.E, self.I, self.H
-        # the router's rows, and behind them the row of the shared expert's gate: one product with a 32-bit result
-        self.w_router = make(n["router"], ParamDecl((self.R + (1 if self.shared_gate else 0), H)))
+        # the router's rows, and behind them the row of the shared expert's gate: one product with a 32-bit result.
+        # Rows of zeros fill the matrix up to a multiple of 8, so that the result's rows start on 16-byte borders
+        # (the library has no fast product for other strides)
+        used = self.R + (1 if self.shared_gate else 0)
+        self.w_router = make(n["router"], ParamDecl((-(-used // 8) * 8, H)))
+        self.w_router[used:].zero_()
         self.tensors[n["router"]] = self.w_router[:self.R]
         if self.shared_gate:
-            self.tensors[n["shared_gate"]] = self.w_router[self.R:]
+            self.tensors[n["shared_gate"]] = self.w_router[self.R:used]
         self.w_correction = None
         if self.correction:
             self.w_correction = self.tensors[n["correction"]] = make(n["correction"], ParamDecl((self.R,), "bias32"))
@@ -124,7 +128,7 @@ class RoutedExperts(FeedForward):
         K.moe_grouped_linear(act, self.w_down, offsets, order, None, rows, top, False, False)
         shared = None
         if self.shared is not None:
-            shared = (self.shared.forward(x, ctx), logits[:, self.R:] if self.shared_gate else None)
+            shared = (self.shared.forward(x, ctx), logits[:, self.R:self.R + 1] if self.shared_gate else None)
         # (a buffer of its own: the shared expert's output may lie in "ffn.out")
         out = ws.tokens("moe.out", T, self.H, x.dtype)
         K.moe_combine(rows, place, None if on_input else weight, out, top,
