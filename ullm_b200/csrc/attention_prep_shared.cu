@@ -143,11 +143,13 @@ __global__ void pool_blocks_kernel(const int* __restrict__ positions, const int*
   }
 }
 
-// One block per token.  q_full [tokens][heads][dim + rot] (the query up-projection), q_lat [heads][tokens][rank]
-// (q_h W_uk,h), dkv [tokens][rank + rot]; q_out [tokens][heads][rank + rot]; key pages [*][rank + rot].
+// One block per token.  q_full [tokens][heads][dim + rot] (the query projection; rows `q_stride` apart), q_lat
+// [heads][tokens][rank] (q_h W_uk,h; null: already in q_out), dkv [tokens][rank + rot] (rows `dkv_stride` apart);
+// q_out [tokens][heads][rank + rot]; key pages [*][rank + rot].
 template <typename T>
-__global__ void latent_prepare_kernel(const T* __restrict__ q_full, const T* __restrict__ q_lat,
-                                      const T* __restrict__ dkv, T* __restrict__ q_out, int tokens, int heads,
+__global__ void latent_prepare_kernel(const T* __restrict__ q_full, long long q_stride, const T* __restrict__ q_lat,
+                                      const T* __restrict__ dkv, long long dkv_stride, T* __restrict__ q_out,
+                                      int tokens, int heads,
                                       int dim, int rot, int rank, int rot_dims, int interleaved,
                                       const float* __restrict__ w_c, float eps, const float* __restrict__ inv_freq,
                                       const int* __restrict__ positions, const int* __restrict__ slot_mapping,
@@ -159,14 +161,16 @@ __global__ void latent_prepare_kernel(const T* __restrict__ q_full, const T* __r
   const float p = (float)positions[t];
   const int kw = rank + rot;
   const int half = rot_dims >> 1;
-  // queries: the absorbed part is copied, the rotated part turned
-  for (int i = threadIdx.x; i < heads * rank; i += blockDim.x) {
-    const int h = i / rank, c = i - h * rank;
-    q_out[((long long)t * heads + h) * kw + c] = q_lat[((long long)h * tokens + t) * rank + c];
+  // queries: the absorbed part is copied (unless the product in front wrote it in place), the rotated part turned
+  if (q_lat != nullptr) {
+    for (int i = threadIdx.x; i < heads * rank; i += blockDim.x) {
+      const int h = i / rank, c = i - h * rank;
+      q_out[((long long)t * heads + h) * kw + c] = q_lat[((long long)h * tokens + t) * rank + c];
+    }
   }
   for (int i = threadIdx.x; i < heads * rot; i += blockDim.x) {
     const int h = i / rot, c = i - h * rot;
-    const T* src = q_full + ((long long)t * heads + h) * (dim + rot) + dim;
+    const T* src = q_full + (long long)t * q_stride + (long long)h * (dim + rot) + dim;
     float v = to_f32(src[c]);
     if (c < rot_dims) {
       const bool second = interleaved ? (c & 1) : (c >= half);
@@ -184,7 +188,7 @@ __global__ void latent_prepare_kernel(const T* __restrict__ q_full, const T* __r
     if (threadIdx.x == 0) ullm_report(status, ULLM_STATUS_SLOT, t, (int)slot);
     slot = -1;
   }
-  const T* row = dkv + (long long)t * kw;
+  const T* row = dkv + (long long)t * dkv_stride;
   float acc = 0.f;
   for (int c = threadIdx.x; c < rank; c += blockDim.x) {
     const float v = to_f32(row[c]);
@@ -472,18 +476,23 @@ extern "C" int ullm_pool_blocks(int dtype, const int* positions, const int* toke
   return ULLM_ERR_BAD_DTYPE;
 }
 
+// `q_stride` / `dkv_stride`: elements between two tokens' rows of q_full / dkv (0: dense rows).
 extern "C" int ullm_latent_prepare(int dtype, const void* q_full, const void* q_lat, const void* dkv, void* q_out,
                                    int tokens, int heads, int dim, int rot, int rank, int rot_dims, const float* w_c,
                                    float eps, const float* inv_freq, const int* positions, const int* slot_mapping,
-                                   void* k_pages, long long num_slots, int* status, void* stream, int interleaved) {
+                                   void* k_pages, long long num_slots, int* status, void* stream, int interleaved,
+                                   long long q_stride, long long dkv_stride) {
   cudaStream_t st = (cudaStream_t)stream;
   if (tokens < 0 || heads <= 0 || dim <= 0 || rot < 0 || rank <= 0) return ULLM_ERR_BAD_SIZE;
+  if (q_stride == 0) q_stride = (long long)heads * (dim + rot);
+  if (dkv_stride == 0) dkv_stride = rank + rot;
+  if (q_stride < (long long)heads * (dim + rot) || dkv_stride < rank + rot) return ULLM_ERR_BAD_SIZE;
   if (rot_dims < 0 || rot_dims > rot || rot_dims % 2 || (rot_dims > 0 && inv_freq == nullptr)) return ULLM_ERR_BAD_SIZE;
   if (tokens == 0) return ULLM_OK;
   const dim3 grid(tokens), block(prep_threads(heads * rank / 4));
 #define LP_GO(T)                                                                                                  \
-  return ullm_launch_kernel(latent_prepare_kernel<T>, grid, block, 0, st, (const T*)q_full, (const T*)q_lat,       \
-                            (const T*)dkv, (T*)q_out, tokens, heads, dim, rot, rank, rot_dims, interleaved, w_c, eps,  \
+  return ullm_launch_kernel(latent_prepare_kernel<T>, grid, block, 0, st, (const T*)q_full, q_stride,              \
+                            (const T*)q_lat, (const T*)dkv, dkv_stride, (T*)q_out, tokens, heads, dim, rot, rank, rot_dims, interleaved, w_c, eps,  \
                             inv_freq, positions, slot_mapping, (T*)k_pages, num_slots, status)
   if (dtype == ULLM_DTYPE_F32) LP_GO(float);
   if (dtype == ULLM_DTYPE_BF16) LP_GO(__nv_bfloat16);

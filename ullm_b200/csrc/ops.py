@@ -268,7 +268,7 @@ class Kernels:
             "ullm_xielu": [I, P, P, LL, P, P],
             "ullm_kv_shared_prepare": [I, P, LL, I, I, I, P, P, F, P, P, P, LL, P, P],
             "ullm_pool_blocks": [I, P, P, P, P, I, I, LL, P, P, I, I, P, LL, P, P, I, I, P, P],
-            "ullm_latent_prepare": [I, P, P, P, P, I, I, I, I, I, I, P, F, P, P, P, P, LL, P, P, I],
+            "ullm_latent_prepare": [I, P, P, P, P, I, I, I, I, I, I, P, F, P, P, P, P, LL, P, P, I, LL, LL],
             "ullm_qkv_rows_prepare": [I, P, LL, P, I, I, I, I, I, P, P, F, P, I, I, P, P, I, P, P, P, LL, P, P],
             "ullm_concat_rows_f32": [I, P, P, P, I, I, I, P],
             "ullm_sigmoid_gate": [I, P, P, LL, I, I, P],
@@ -970,17 +970,23 @@ class Kernels:
     def latent_prepare(self, q_full, q_lat, dkv, q_out, heads: int, dim: int, rot: int, rank: int, rot_dims: int, c_w,
                        eps: float, inv_freq, positions, slot_mapping, k_pages, interleaved: bool = True):
         """Latent attention, absorbed form.  q_full [T, heads x (dim + rot)], q_lat [heads, T, rank] (each head's
-        unrotated query times its key up-projection), dkv [T, rank + rot].  Leaves q_out [T, heads x (rank + rot)]
+        unrotated query times its key up-projection; None: the product wrote it into q_out itself), dkv
+        [T, rank + rot]; q_full and dkv may be column ranges of wider rows.  Leaves q_out [T, heads x (rank + rot)]
         = [q_lat | rotated q_rot] per head and the key row [RMSnorm(dkv[:rank]) x c_w | rotated dkv[rank:]] in
         `k_pages` at the tokens' slots.  Neighbouring dimensions (2i, 2i + 1) below `rot_dims` are rotated, or
         without `interleaved` the dimensions (i, i + rot_dims / 2)."""
         T = dkv.shape[0]
-        for t, n in ((q_full, "q_full"), (q_lat, "q_lat"), (dkv, "dkv"), (q_out, "q_out"), (k_pages, "k_pages")):
+        for t, n in ((q_full, "q_full"), (dkv, "dkv")):
+            _need(t, n, dkv.dtype, contiguous=False)
+            if t.stride(1) != 1:
+                raise KernelError(f"latent_prepare: {n} needs unit stride inside its rows")
+        for t, n in ((q_out, "q_out"), (k_pages, "k_pages")) + (((q_lat, "q_lat"),) if q_lat is not None else ()):
             _need(t, n, dkv.dtype)
         _need(c_w, "c_w", torch.float32)
         _need(positions, "positions", torch.int32)
-        if (q_full.shape != (T, heads * (dim + rot)) or q_lat.shape != (heads, T, rank) or dkv.shape[1] != rank + rot
-                or q_out.shape != (T, heads * (rank + rot)) or c_w.numel() != rank or k_pages.shape[-1] != rank + rot):
+        if (q_full.shape != (T, heads * (dim + rot)) or (q_lat is not None and q_lat.shape != (heads, T, rank))
+                or dkv.shape[1] != rank + rot or q_out.shape != (T, heads * (rank + rot)) or c_w.numel() != rank
+                or k_pages.shape[-1] != rank + rot):
             raise KernelError("latent_prepare: shapes do not fit the sizes")
         if rot_dims:
             _need(inv_freq, "inv_freq", torch.float32)
@@ -991,7 +997,8 @@ class Kernels:
         self._check(self.lib.ullm_latent_prepare(
             _DT[dkv.dtype], _ptr(q_full), _ptr(q_lat), _ptr(dkv), _ptr(q_out), T, heads, dim, rot, rank, rot_dims,
             _ptr(c_w), float(eps), _ptr(inv_freq), _ptr(positions), _ptr(slot_mapping), _ptr(k_pages),
-            k_pages.numel() // (rank + rot), _ptr(self.status), _stream(), int(bool(interleaved))), "latent_prepare")
+            k_pages.numel() // (rank + rot), _ptr(self.status), _stream(), int(bool(interleaved)), q_full.stride(0),
+            dkv.stride(0)), "latent_prepare")
 
     @_timed("qk_norm_rope_store")
     def qkv_rows_prepare(self, qkv, q_out, num_q: int, num_kv: int, head_dim: int, v_dim: int, positions, slot_mapping,

@@ -227,9 +227,21 @@ class LatentAttention(Mixer):
         return d
 
     def materialize(self, make):
-        super().materialize(make)
+        n, N, H = self.names, self.num_heads, self.hidden_size
+        self.w_in = None
+        if self.q_rank is None:
+            # one product for q | latent and rotated key part | output gate, all read from the mixer's input
+            qw = N * (self.head_dim + self.rot_dim)
+            self.w_in = make("in_proj.weight", ParamDecl((qw + self.key_row + (N * self.value_dim if self.gated else 0), H)))
+            self.tensors[n["q"]] = self.w_in[:qw]
+            self.tensors[n["dkv"]] = self.w_in[qw:qw + self.key_row]
+            if self.gated:
+                self.tensors[n["g"]] = self.w_in[qw + self.key_row:]
+        for name, decl in self.param_decls().items():
+            if name not in self.tensors:
+                self.tensors[name] = make(name, decl)
         if self.position is not None:
-            self.position.build_tables(self.tensors[self.names["dkv"]].device)
+            self.position.build_tables(self.tensors[n["dkv"]].device)
 
     def cache_need(self):
         window = None if self.window is None else max(self.window, self.pool)
@@ -257,22 +269,31 @@ class LatentAttention(Mixer):
         if g is None or not cache.writes:
             raise RuntimeError("latent attention keeps a cache of its own: it was given none to write")
         dt = x.dtype
-        q_full = ws.tokens("lat.q", T, N * (d + r), dt)
-        if self.q_rank is None:
-            linear(x, self.tensors[n["q"]], q_full)
+        gate = None
+        if self.w_in is not None:
+            qw = N * (d + r)
+            both = ws.tokens("lat.in", T, self.w_in.shape[0], dt)
+            linear(x, self.w_in, both)
+            q_full, dkv = both[:, :qw], both[:, qw:qw + self.key_row]
+            gate = both[:, qw + self.key_row:] if self.gated else None
         else:
+            q_full = ws.tokens("lat.q", T, N * (d + r), dt)
             cq = ws.tokens("lat.cq", T, self.q_rank, dt)
             linear(x, self.tensors[n["dq"]], cq)
             K.add_rmsnorm(cq, None, self.tensors[n["dq_norm"]], self.norm_eps, cq)
             linear(cq, self.tensors[n["uq"]], q_full)
-        dkv = ws.tokens("lat.dkv", T, self.key_row, dt)
-        linear(x, self.tensors[n["dkv"]], dkv)
-        # every head's unrotated query through its key up-projection: [heads, T, dim] x [heads, dim, rank]
-        q_lat = ws.tokens("lat.q_lat", N * T, R, dt).view(N, T, R)
-        batched_matmul(q_full.view(T, N, d + r)[:, :, :d].transpose(0, 1), self.tensors[n["uk"]].view(N, d, R), q_lat)
+            dkv = ws.tokens("lat.dkv", T, self.key_row, dt)
+            linear(x, self.tensors[n["dkv"]], dkv)
+            if self.gated:
+                gate = ws.tokens("lat.gate", T, N * dv, dt)
+                linear(x, self.tensors[n["g"]], gate)
+        # every head's unrotated query through its key up-projection, [heads, T, dim] x [heads, dim, rank], written
+        # straight into the absorbed part of the query rows [T, heads, rank | rot]
         q_out = ws.tokens("lat.q_out", T, N * self.key_row, dt)
+        batched_matmul(q_full.unflatten(1, (N, d + r))[:, :, :d].transpose(0, 1), self.tensors[n["uk"]].view(N, d, R),
+                       q_out.view(T, N, self.key_row)[:, :, :R].transpose(0, 1))
         tables = self.position.tables() if self.position is not None else {}
-        K.latent_prepare(q_full, q_lat, dkv, q_out, N, d, r, R, self.position.rotary_dim if self.position else 0,
+        K.latent_prepare(q_full, None, dkv, q_out, N, d, r, R, self.position.rotary_dim if self.position else 0,
                          self.tensors[n["dkv_norm"]], self.norm_eps, tables.get("inv_freq"), ctx.positions,
                          g.slot_mapping, cache.k_pages, interleaved=bool(getattr(self.position, "interleaved", True)))
         pooled = None
@@ -291,9 +312,7 @@ class LatentAttention(Mixer):
         attn = ws.tokens("attn.out", T, N * dv, dt)
         batched_matmul(o_lat.view(T, N, R).transpose(0, 1), self.tensors[n["uv"]].view(N, dv, R).transpose(1, 2),
                        attn.view(T, N, dv).transpose(0, 1))
-        if self.gated:
-            gate = ws.tokens("lat.gate", T, N * dv, dt)
-            linear(x, self.tensors[n["g"]], gate)
+        if gate is not None:
             K.sigmoid_gate(attn, gate)
         out = ws.tokens("mixer.out", T, self.hidden_size, dt)
         linear(attn, self.tensors[n["o"]], out)
