@@ -302,6 +302,16 @@ __global__ void qkv_rows_prepare_kernel(const T* __restrict__ qkv, long long str
   }
 }
 
+// Two neighbouring elements in one store (the pair starts at an even element of a 4-byte aligned row: q_size,
+// k_size and the channel are even, the buffers come from the allocator).
+__device__ __forceinline__ void store_pair(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+__device__ __forceinline__ void store_pair(__half* p, float a, float b) {
+  *reinterpret_cast<__half2*>(p) = __floats2half2_rn(a, b);
+}
+
 // The same work with the token's row staged once in shared memory as 32-bit values (16-byte loads where the rows
 // allow), the sums of squares formed while it is staged, and q and k handled two neighbouring channels at a time
 // (a rotation of neighbours then needs no second read; paired stores).  Needs an even head size; `row` holds
@@ -315,7 +325,7 @@ __global__ void qkv_rows_prepare_staged_kernel(const T* __restrict__ qkv, long l
                                                const float* __restrict__ q_head_scale, int v_unit,
                                                const int* __restrict__ slot_mapping, T* __restrict__ k_pages,
                                                T* __restrict__ v_pages, long long num_slots, int wide, int* status) {
-  extern __shared__ float prep_row[];
+  extern __shared__ __align__(16) float prep_row[];
   __shared__ float scratch[33];
   __shared__ float cs_s[ROWS_MAX_ROT / 2], sn_s[ROWS_MAX_ROT / 2];
   pdl_launch_dependents();
@@ -340,13 +350,16 @@ __global__ void qkv_rows_prepare_staged_kernel(const T* __restrict__ qkv, long l
     for (int c = threadIdx.x * VEC; c < width; c += blockDim.x * VEC) {
       const uint4 raw = *reinterpret_cast<const uint4*>(src + c);
       const T* e = reinterpret_cast<const T*>(&raw);
+      float xs[VEC];
       float sq = 0.f;
 #pragma unroll
       for (int i = 0; i < VEC; ++i) {
-        const float x = to_f32(e[i]);
-        prep_row[c + i] = x;
-        sq += x * x;
+        xs[i] = to_f32(e[i]);
+        sq += xs[i] * xs[i];
       }
+#pragma unroll
+      for (int i = 0; i < VEC; i += 4)  // (c is a multiple of VEC, the array 16-byte aligned)
+        *reinterpret_cast<float4*>(prep_row + c + i) = make_float4(xs[i], xs[i + 1], xs[i + 2], xs[i + 3]);
       if (c < q_size) acc_q += sq;
       else if (c < q_size + k_size) acc_k += sq;
     }
@@ -365,17 +378,21 @@ __global__ void qkv_rows_prepare_staged_kernel(const T* __restrict__ qkv, long l
   } else {
     __syncthreads();
   }
+  const float inv_head_dim = 1.f / (float)head_dim;
   // q and k, two neighbouring channels per thread
   for (int c = threadIdx.x * 2; c < q_size + k_size; c += blockDim.x * 2) {
     const bool is_q = c < q_size;
     const int cc = is_q ? c : c - q_size;
     const float* w = is_q ? wq : wk;
     const float r = is_q ? rq : rk;
-    const int h = cc / head_dim, j = cc - h * head_dim;  // (j is even, j + 1 in the same head)
-    float x0 = prep_row[c] * r, x1 = prep_row[c + 1] * r;
+    // (the head by a product: (cc + 1/2) / head_dim is at least 1 / (2 head_dim) away from a whole number)
+    const int h = __float2int_rd(((float)cc + 0.5f) * inv_head_dim), j = cc - h * head_dim;  // (j even, j + 1 in the head)
+    const float2 xr = *reinterpret_cast<const float2*>(prep_row + c);
+    float x0 = xr.x * r, x1 = xr.y * r;
     if (w != nullptr) {
-      x0 *= w[cc];
-      x1 *= w[cc + 1];
+      const float2 ww = *reinterpret_cast<const float2*>(w + cc);  // (cc is even, the weights 8-byte aligned)
+      x0 *= ww.x;
+      x1 *= ww.y;
     }
     if (j < rot_dims) {
       if (interleaved) {
@@ -404,13 +421,9 @@ __global__ void qkv_rows_prepare_staged_kernel(const T* __restrict__ qkv, long l
         x0 *= q_head_scale[h];
         x1 *= q_head_scale[h];
       }
-      T* dst = q_out + (long long)t * q_size + cc;
-      dst[0] = from_f32<T>(x0);
-      dst[1] = from_f32<T>(x1);
+      store_pair(q_out + (long long)t * q_size + cc, x0, x1);
     } else if (slot >= 0) {
-      T* dst = k_pages + slot * k_size + cc;
-      dst[0] = from_f32<T>(x0);
-      dst[1] = from_f32<T>(x1);
+      store_pair(k_pages + slot * k_size + cc, x0, x1);
     }
   }
   if (slot < 0) return;
@@ -519,7 +532,9 @@ extern "C" int ullm_qkv_rows_prepare(int dtype, const void* qkv, long long strid
   const dim3 grid(tokens), block(prep_threads(num_q * head_dim / 4));
   const long long width = (long long)num_q * head_dim + (long long)num_kv * (head_dim + v_dim);
   const size_t smem = (size_t)width * sizeof(float);
-  if (head_dim % 2 == 0 && smem <= 160 * 1024) {
+  const bool pairs_ok = (((uintptr_t)wq | (uintptr_t)wk) % 8 == 0) &&
+                        (((uintptr_t)q_out | (uintptr_t)k_pages) % 8 == 0);
+  if (head_dim % 2 == 0 && smem <= 160 * 1024 && pairs_ok) {
     // the staged form: the row waits in shared memory
     const int esize = dtype == ULLM_DTYPE_F32 ? 4 : 2, vec = 16 / esize;
     const int wide = ((uintptr_t)qkv % 16 == 0) && stride % vec == 0 && (num_q * head_dim) % vec == 0 &&
