@@ -71,6 +71,7 @@ __global__ void kv_shared_prepare_kernel(T* __restrict__ qk, long long stride, i
 }
 
 #define POOL_SLOTS 1024
+#define ROWS_MAX_ROT 512  // rotated dimensions whose angles a block keeps in shared memory
 
 // One block per token; a token whose pooled slot is -1 completes no block.  The block's positions are
 // pos - pool + 1 .. pos of the token's request, found through the request's row of the block table.
@@ -157,10 +158,14 @@ __global__ void latent_prepare_kernel(const T* __restrict__ q_full, long long q_
   __shared__ float scratch[33];
   pdl_launch_dependents();
   pdl_wait();
+  __shared__ float cs_s[ROWS_MAX_ROT / 2], sn_s[ROWS_MAX_ROT / 2];
   const int t = blockIdx.x;
   const float p = (float)positions[t];
   const int kw = rank + rot;
   const int half = rot_dims >> 1;
+  // the token's angles once (the launcher refuses more rotated dimensions than the arrays hold)
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(p * inv_freq[i], &sn_s[i], &cs_s[i]);
+  __syncthreads();
   // queries: the absorbed part is copied (unless the product in front wrote it in place), the rotated part turned
   if (q_lat != nullptr) {
     for (int i = threadIdx.x; i < heads * rank; i += blockDim.x) {
@@ -175,8 +180,8 @@ __global__ void latent_prepare_kernel(const T* __restrict__ q_full, long long q_
     if (c < rot_dims) {
       const bool second = interleaved ? (c & 1) : (c >= half);
       const int pc = interleaved ? (c ^ 1) : (second ? c - half : c + half);
-      float sn, cs;
-      sincosf(p * inv_freq[interleaved ? (c >> 1) : (second ? c - half : c)], &sn, &cs);
+      const int fi = interleaved ? (c >> 1) : (second ? c - half : c);
+      const float sn = sn_s[fi], cs = cs_s[fi];
       const float other = to_f32(src[pc]);
       v = second ? v * cs + other * sn : v * cs - other * sn;
     }
@@ -203,16 +208,14 @@ __global__ void latent_prepare_kernel(const T* __restrict__ q_full, long long q_
     if (c < rot_dims) {
       const bool second = interleaved ? (c & 1) : (c >= half);
       const int pc = interleaved ? (c ^ 1) : (second ? c - half : c + half);
-      float sn, cs;
-      sincosf(p * inv_freq[interleaved ? (c >> 1) : (second ? c - half : c)], &sn, &cs);
+      const int fi = interleaved ? (c >> 1) : (second ? c - half : c);
+      const float sn = sn_s[fi], cs = cs_s[fi];
       const float other = to_f32(row[rank + pc]);
       v = second ? v * cs + other * sn : v * cs - other * sn;
     }
     dst[rank + c] = from_f32<T>(v);
   }
 }
-
-#define ROWS_MAX_ROT 512
 
 // One block per token.  qkv [tokens][stride]: q (num_q heads of head_dim) | k (num_kv heads of head_dim) | v (num_kv
 // heads of v_dim) as projected; q_out [tokens][num_q * head_dim].
@@ -326,7 +329,7 @@ __global__ void qkv_rows_prepare_staged_kernel(const T* __restrict__ qkv, long l
                                                const int* __restrict__ slot_mapping, T* __restrict__ k_pages,
                                                T* __restrict__ v_pages, long long num_slots, int wide, int* status) {
   extern __shared__ __align__(16) float prep_row[];
-  __shared__ float scratch[33];
+  __shared__ float scratch2[64];
   __shared__ float cs_s[ROWS_MAX_ROT / 2], sn_s[ROWS_MAX_ROT / 2];
   pdl_launch_dependents();
   pdl_wait();
@@ -373,8 +376,20 @@ __global__ void qkv_rows_prepare_staged_kernel(const T* __restrict__ qkv, long l
   }
   float rq = 1.f, rk = 1.f;
   if (wq != nullptr) {
-    rq = 1.f / sqrtf(block_sum(acc_q, scratch) / (float)q_size + eps);
-    rk = 1.f / sqrtf(block_sum(acc_k, scratch) / (float)k_size + eps);
+    // both sums in one round of barriers (the order of additions depends only on the block's size)
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    acc_q = warp_sum(acc_q);
+    acc_k = warp_sum(acc_k);
+    if (lane == 0) {
+      scratch2[warp] = acc_q;
+      scratch2[32 + warp] = acc_k;
+    }
+    __syncthreads();
+    float tq = lane < nwarps ? scratch2[lane] : 0.f, tk = lane < nwarps ? scratch2[32 + lane] : 0.f;
+    tq = warp_sum(tq);
+    tk = warp_sum(tk);
+    rq = 1.f / sqrtf(tq / (float)q_size + eps);
+    rk = 1.f / sqrtf(tk / (float)k_size + eps);
   } else {
     __syncthreads();
   }
@@ -501,6 +516,7 @@ extern "C" int ullm_latent_prepare(int dtype, const void* q_full, const void* q_
   if (dkv_stride == 0) dkv_stride = rank + rot;
   if (q_stride < (long long)heads * (dim + rot) || dkv_stride < rank + rot) return ULLM_ERR_BAD_SIZE;
   if (rot_dims < 0 || rot_dims > rot || rot_dims % 2 || (rot_dims > 0 && inv_freq == nullptr)) return ULLM_ERR_BAD_SIZE;
+  if (rot_dims > ROWS_MAX_ROT) return ULLM_ERR_UNSUPPORTED;
   if (tokens == 0) return ULLM_OK;
   const dim3 grid(tokens), block(prep_threads(heads * rank / 4));
 #define LP_GO(T)                                                                                                  \
@@ -534,6 +550,7 @@ extern "C" int ullm_qkv_rows_prepare(int dtype, const void* qkv, long long strid
   const size_t smem = (size_t)width * sizeof(float);
   const bool pairs_ok = (((uintptr_t)wq | (uintptr_t)wk) % 8 == 0) &&
                         (((uintptr_t)q_out | (uintptr_t)k_pages) % 8 == 0);
+  const dim3 staged_block(block.x);  // (128 threads, all blocks of a 2,048-token step resident at once: no faster)
   if (head_dim % 2 == 0 && smem <= 160 * 1024 && pairs_ok) {
     // the staged form: the row waits in shared memory
     const int esize = dtype == ULLM_DTYPE_F32 ? 4 : 2, vec = 16 / esize;
@@ -546,7 +563,7 @@ extern "C" int ullm_qkv_rows_prepare(int dtype, const void* qkv, long long strid
       cudaGetLastError();                                                                                            \
       return ULLM_ERR_LAUNCH;                                                                                        \
     }                                                                                                                \
-    return ullm_launch_kernel(qkv_rows_prepare_staged_kernel<T>, grid, block, smem, st, (const T*)qkv, stride,       \
+    return ullm_launch_kernel(qkv_rows_prepare_staged_kernel<T>, grid, staged_block, smem, st, (const T*)qkv, stride, \
                               (T*)q_out, num_q, num_kv, head_dim, v_dim, wq, wk, eps, inv_freq, rot_dims,            \
                               interleaved, positions, q_head_scale, v_unit, slot_mapping, (T*)k_pages, (T*)v_pages,  \
                               num_slots, wide, status);                                                              \
