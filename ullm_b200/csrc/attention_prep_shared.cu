@@ -376,7 +376,7 @@ __global__ void qkv_rows_prepare_staged_kernel(const T* __restrict__ qkv, long l
   }
   float rq = 1.f, rk = 1.f;
   if (wq != nullptr) {
-    // both sums in one round of barriers (the order of additions depends only on the block's size)
+    // both sums in one set of barriers (the order of additions depends only on the block's size)
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
     acc_q = warp_sum(acc_q);
     acc_k = warp_sum(acc_k);
