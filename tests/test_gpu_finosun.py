@@ -108,6 +108,36 @@ def test_every_feed_forward_alone(tmp_path, dtype, tag):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("tag", ["A", "C", "E"])
+def test_a_feed_forward_adds_itself_to_the_stream_as_the_separate_kernels_do(tmp_path, dtype, tag):
+    """The routed feed-forward's last kernel in its form that adds to the 32-bit stream with a scale per channel and
+    leaves the next norm's rows, against the plain feed-forward, the sum and the norm in 64-bit; the rows of the
+    next norm may overwrite the feed-forward's own input."""
+    cfg, w, page = weights_for(tag, dtype)
+    cfg = cfg if dtype == "float32" else every_output_chosen(cfg)
+    r = make_runner(tmp_path, cfg, w, page, dtype)
+    W = cfg["width"]
+    x = rand((19, W), 8, dtype, 1.5)
+    wd = {k: t.double() for k, t in w.items()}
+    g = torch.Generator().manual_seed(4)
+    stream0 = torch.randn(19, W, generator=g)
+    scale = 0.5 + torch.rand(W, generator=g)
+    w2 = 1.0 + 0.2 * torch.randn(W, generator=g)
+    for l, L in enumerate(cfg["layers"]):
+        if L["mlp"] is None:
+            continue
+        ref = stream0.double() + scale.double() * pf.routed_ff(x.double().cpu(), L["mlp"], wd, f"l{l}.mlp.")
+        ref_norm = pf.rms_norm(ref, w2.double(), 3e-6)
+        stream = stream0.clone().to(device())
+        rows = x.clone()  # (the next norm's rows take the input's place)
+        ok = r.model.blocks[l].feed_forward.forward_add(rows, _ctx_for(r), stream, scale.to(device()),
+                                                        (w2.to(device()), 3e-6, rows))
+        assert ok
+        close(stream, ref.float(), dtype, f"{tag} layer {l}: stream")
+        close(rows, ref_norm.float(), dtype, f"{tag} layer {l}: next norm")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_large_correction_decides_the_choice_but_not_the_weight(tmp_path, dtype):
     """One router output gets a correction far above every score: every token takes it, with its own small score as
     the weight; once it is a real expert, once a passing one."""

@@ -438,6 +438,85 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __rest
   }
 }
 
+// The same sum, added to a 32-bit residual stream instead of stored, with a scale per channel, and followed by the
+// RMS norm that reads the stream next:  stream[t] += scale * y[t];  out[t] = w2 * stream[t] / sqrt(mean(stream[t]^2) +
+// eps2).  One block per token; the sum never leaves 32-bit.  `x` (the passing experts' input) and `out` may be the
+// same rows: a block reads its token's row of x before the barrier and writes its row of out behind it.
+template <typename T, int VEC>
+__global__ void moe_combine_add_norm_kernel(const T* __restrict__ rows, const int* __restrict__ place,
+                                            const float* __restrict__ pair_weight, int top, int cols,
+                                            const int* __restrict__ choice, int experts, const T* x,
+                                            long long x_stride, const T* __restrict__ shared_rows,
+                                            const float* __restrict__ shared_gate, long long gate_stride,
+                                            float* __restrict__ stream, const float* __restrict__ scale,
+                                            const float* __restrict__ w2, float eps2, T* out) {
+  extern __shared__ __align__(16) float mc_row[];
+  __shared__ float scratch[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long t = blockIdx.x;
+  const float sg = (shared_rows != nullptr && shared_gate != nullptr)
+                       ? 1.f / (1.f + expf(-shared_gate[t * gate_stride])) : 1.f;
+  float sq = 0.f;
+  for (int c0 = threadIdx.x * VEC; c0 < cols; c0 += blockDim.x * VEC) {
+    float acc[VEC], v[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const long long pair = t * top + k;
+      const bool passes = choice != nullptr && choice[pair] >= experts;
+      const T* src = passes ? x + t * x_stride : rows + (long long)place[pair] * cols;
+      moe_load_vec<T, VEC>(src + c0, v);
+      const float w = pair_weight != nullptr ? pair_weight[pair] : 1.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] += w * v[i];
+    }
+    if (shared_rows != nullptr) {
+      moe_load_vec<T, VEC>(shared_rows + t * cols + c0, v);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] += sg * v[i];
+    }
+    if constexpr (VEC % 4 == 0) {
+      // (c0 is a multiple of VEC, cols too: 16-byte pieces of the stream, the scale and the row in shared memory)
+#pragma unroll
+      for (int i = 0; i < VEC; i += 4) {
+        float4 s4 = *reinterpret_cast<const float4*>(stream + t * cols + c0 + i);
+        float4 sc = make_float4(1.f, 1.f, 1.f, 1.f);
+        if (scale != nullptr) sc = *reinterpret_cast<const float4*>(scale + c0 + i);
+        s4.x += sc.x * acc[i];
+        s4.y += sc.y * acc[i + 1];
+        s4.z += sc.z * acc[i + 2];
+        s4.w += sc.w * acc[i + 3];
+        *reinterpret_cast<float4*>(stream + t * cols + c0 + i) = s4;
+        *reinterpret_cast<float4*>(mc_row + c0 + i) = s4;
+        sq += s4.x * s4.x + s4.y * s4.y + s4.z * s4.z + s4.w * s4.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
+        const int c = c0 + i;
+        const float s = stream[t * cols + c] + (scale != nullptr ? scale[c] : 1.f) * acc[i];
+        stream[t * cols + c] = s;
+        mc_row[c] = s;
+        sq += s * s;
+      }
+    }
+  }
+  if (out == nullptr) return;
+  const float rstd = 1.f / sqrtf(block_sum(sq, scratch) / (float)cols + eps2);
+  if constexpr (VEC * sizeof(T) == 16) {
+    for (int c0 = threadIdx.x * VEC; c0 < cols; c0 += blockDim.x * VEC) {
+      uint4 raw;
+      T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) e[i] = from_f32<T>(mc_row[c0 + i] * rstd * w2[c0 + i]);
+      *reinterpret_cast<uint4*>(out + t * cols + c0) = raw;
+    }
+  } else {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) out[t * cols + c] = from_f32<T>(mc_row[c] * rstd * w2[c]);
+  }
+}
+
 static int g_moe_force_plain = 0;
 // 1: the grouped product never takes the tensor-core kernel (tests compare the two)
 extern "C" void ullm_moe_force_plain(int on) { g_moe_force_plain = on ? 1 : 0; }
@@ -565,5 +644,55 @@ extern "C" int ullm_moe_combine(int dtype, const void* rows, const int* place, c
     MC_GO(__half, 1);
   }
 #undef MC_GO
+  return ULLM_ERR_BAD_DTYPE;
+}
+
+// stream (32-bit, [tokens, cols], in place) += scale * (the sum `ullm_moe_combine` forms); `scale` null: 1.  `out` with
+// `w2` (null: none): the RMS norm of the updated rows, in the rows' dtype; `out` may be `x`.
+extern "C" int ullm_moe_combine_add_norm(int dtype, const void* rows, const int* place, const float* pair_weight,
+                                         int tokens, int top, int cols, const int* choice, int experts, const void* x,
+                                         long long x_stride, const void* shared_rows, const float* shared_gate,
+                                         long long gate_stride, float* stream_rows, const float* scale,
+                                         const float* w2, float eps2, void* out, void* stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (tokens < 0 || top <= 0 || cols <= 0 || stream_rows == nullptr) return ULLM_ERR_BAD_SIZE;
+  if (choice != nullptr && (x == nullptr || x_stride < cols || experts < 0)) return ULLM_ERR_BAD_SIZE;
+  if (out != nullptr && w2 == nullptr) return ULLM_ERR_BAD_SIZE;
+  const size_t smem = (size_t)cols * sizeof(float);
+  if (smem > 160 * 1024) return ULLM_ERR_UNSUPPORTED;
+  if (tokens == 0) return ULLM_OK;
+  const int esize = dtype == ULLM_DTYPE_F32 ? 4 : 2;
+  const int vec = 16 / esize;
+  const bool wide = cols % vec == 0 && x_stride % vec == 0 &&
+                    (((uintptr_t)rows | (uintptr_t)x | (uintptr_t)shared_rows | (uintptr_t)stream_rows |
+                      (uintptr_t)scale | (uintptr_t)w2 | (uintptr_t)out) & 15) == 0;
+  const int per_thread = wide ? vec : 1;
+  int threads = 32;
+  while (threads < 256 && threads * per_thread < cols) threads <<= 1;
+  const dim3 grid(tokens), block(threads);
+#define MCA_GO(T, V)                                                                                                   \
+  {                                                                                                                    \
+    if (smem > 48 * 1024 && cudaFuncSetAttribute(moe_combine_add_norm_kernel<T, V>,                                    \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { \
+      cudaGetLastError();                                                                                              \
+      return ULLM_ERR_LAUNCH;                                                                                          \
+    }                                                                                                                  \
+    return ullm_launch_kernel(moe_combine_add_norm_kernel<T, V>, grid, block, smem, st, (const T*)rows, place,         \
+                              pair_weight, top, cols, choice, experts, (const T*)x, x_stride, (const T*)shared_rows,   \
+                              shared_gate, gate_stride, stream_rows, scale, w2, eps2, (T*)out);                        \
+  }
+  if (dtype == ULLM_DTYPE_F32) {
+    if (wide) MCA_GO(float, 4);
+    MCA_GO(float, 1);
+  }
+  if (dtype == ULLM_DTYPE_BF16) {
+    if (wide) MCA_GO(__nv_bfloat16, 8);
+    MCA_GO(__nv_bfloat16, 1);
+  }
+  if (dtype == ULLM_DTYPE_F16) {
+    if (wide) MCA_GO(__half, 8);
+    MCA_GO(__half, 1);
+  }
+#undef MCA_GO
   return ULLM_ERR_BAD_DTYPE;
 }

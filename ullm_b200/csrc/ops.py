@@ -279,6 +279,7 @@ class Kernels:
             "ullm_moe_arrange": [P, I, I, P, P, P, P],
             "ullm_moe_grouped_linear": [I, P, LL, P, LL, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P],
             "ullm_moe_combine": [I, P, P, P, P, I, I, I, P, I, P, LL, P, P, LL, P],
+            "ullm_moe_combine_add_norm": [I, P, P, P, I, I, I, P, I, P, LL, P, P, LL, P, P, P, F, P, P],
             "ullm_argmax": [P, LL, I, I, P, P],
             "ullm_sample": [P, LL, I, I, P, P, P, P, P, P, P, P, P, P],
         }
@@ -1465,6 +1466,30 @@ class Kernels:
         self.lib.ullm_moe_force_plain(1 if on else 0)
 
     @_timed("moe")
+    def _combine_extras(self, what, rows, T, C, top, passing, shared):
+        """Checked (choice, experts, x, x stride, shared rows, shared gate, gate stride) of the two combine calls."""
+        choice = x = s_rows = s_gate = None
+        experts = x_stride = g_stride = 0
+        if passing is not None:
+            choice, experts, x = passing
+            _need(choice, "choice", torch.int32)
+            _need(x, "x", rows.dtype, contiguous=False)
+            if x.shape != (T, C) or x.stride(1) != 1 or choice.numel() < T * top:
+                raise KernelError(f"{what}: the passing experts' input does not fit")
+            x_stride = x.stride(0)
+        if shared is not None:
+            s_rows, s_gate = shared
+            _need(s_rows, "shared rows", rows.dtype)
+            if s_rows.shape != (T, C):
+                raise KernelError(f"{what}: the shared expert's rows do not fit")
+            if s_gate is not None:
+                _need(s_gate, "shared gate", torch.float32, contiguous=False)
+                if s_gate.shape[0] != T:
+                    raise KernelError(f"{what}: one gate number per token")
+                g_stride = s_gate.stride(0)
+        return choice, int(experts), x, x_stride, s_rows, s_gate, g_stride
+
+    @_timed("moe")
     def moe_combine(self, rows, place, pair_weight, y, top: int, passing=None, shared=None):
         """`passing` = (choice, experts, x): a choice at or beyond `experts` adds its weight times the token's row of
         x [T, cols] instead of an expert's row.  `shared` = (rows [T, cols], gate or None): added to every token,
@@ -1475,28 +1500,46 @@ class Kernels:
         T, C = y.shape
         if rows.shape[1] != C or rows.shape[0] < T * top:
             raise KernelError("moe_combine: shapes differ")
-        choice = x = s_rows = s_gate = None
-        experts = x_stride = g_stride = 0
-        if passing is not None:
-            choice, experts, x = passing
-            _need(choice, "choice", torch.int32)
-            _need(x, "x", rows.dtype, contiguous=False)
-            if x.shape != (T, C) or x.stride(1) != 1 or choice.numel() < T * top:
-                raise KernelError("moe_combine: the passing experts' input does not fit")
-            x_stride = x.stride(0)
-        if shared is not None:
-            s_rows, s_gate = shared
-            _need(s_rows, "shared rows", rows.dtype)
-            if s_rows.shape != (T, C):
-                raise KernelError("moe_combine: the shared expert's rows do not fit")
-            if s_gate is not None:
-                _need(s_gate, "shared gate", torch.float32, contiguous=False)
-                if s_gate.shape[0] != T:
-                    raise KernelError("moe_combine: one gate number per token")
-                g_stride = s_gate.stride(0)
+        choice, experts, x, x_stride, s_rows, s_gate, g_stride = self._combine_extras("moe_combine", rows, T, C, top,
+                                                                                      passing, shared)
         self._check(self.lib.ullm_moe_combine(_DT[y.dtype], _ptr(rows), _ptr(place), _ptr(pair_weight), _ptr(y), T, top, C,
-                                              _ptr(choice), int(experts), _ptr(x), x_stride, _ptr(s_rows), _ptr(s_gate),
+                                              _ptr(choice), experts, _ptr(x), x_stride, _ptr(s_rows), _ptr(s_gate),
                                               g_stride, _stream()), "moe_combine")
+
+    @_timed("moe")
+    def moe_combine_add_norm(self, rows, place, pair_weight, top: int, stream, scale=None, next_norm=None, passing=None,
+                             shared=None) -> bool:
+        """stream (float32 [T, cols], in place) += scale * (the sum `moe_combine` forms), the sum kept in 32-bit;
+        `scale` float32 [cols] or None.  `next_norm` = (weight2, eps2, out): out = the RMS norm of the updated rows, in
+        the rows' dtype (it may be the passing experts' x).  False when the kernel does not take the row length
+        (nothing has run then)."""
+        _need(rows, "rows")
+        _need(place, "place", torch.int32)
+        _need(stream, "stream", torch.float32)
+        T, C = stream.shape
+        if rows.shape[1] != C or rows.shape[0] < T * top:
+            raise KernelError("moe_combine_add_norm: shapes differ")
+        if C * 4 > 160 * 1024:
+            return False
+        if scale is not None:
+            _need(scale, "scale", torch.float32)
+            if scale.numel() != C:
+                raise KernelError("moe_combine_add_norm: the scale's length differs from the stream's width")
+        w2 = out = None
+        eps2 = 0.0
+        if next_norm is not None:
+            w2, eps2, out = next_norm
+            _need(w2, "next norm weight", torch.float32)
+            _need(out, "out", rows.dtype)
+            if out.shape != (T, C) or w2.numel() != C:
+                raise KernelError("moe_combine_add_norm: the next norm's shapes differ")
+        choice, experts, x, x_stride, s_rows, s_gate, g_stride = self._combine_extras("moe_combine_add_norm", rows, T, C,
+                                                                                      top, passing, shared)
+        self._check(self.lib.ullm_moe_combine_add_norm(
+            _DT[rows.dtype], _ptr(rows), _ptr(place), _ptr(pair_weight), T, top, C, _ptr(choice), experts, _ptr(x),
+            x_stride, _ptr(s_rows), _ptr(s_gate), g_stride, _ptr(stream), _ptr(scale), _ptr(w2), float(eps2), _ptr(out),
+            _stream()), "moe_combine_add_norm")
+        return True
 
     def check_attention_sizes(self, *a):
         check_attention_sizes(*a)

@@ -216,6 +216,12 @@ class FeedForward(Part):
     def forward(self, x, ctx):
         raise NotImplementedError
 
+    def forward_add(self, x, ctx, stream, scale=None, next_norm=None) -> bool:
+        """Optional: stream (32-bit, in place) += scale * forward(x) in the part's own last kernel (`scale` a
+        32-bit vector per channel or None), which also leaves the RMS norm `next_norm` = (weight, eps, out) of the
+        updated rows.  False (the default): the caller adds `forward(x)` itself."""
+        return False
+
     def gated_weights(self):
         """(w_gate_up [2 I, hidden], w_down [hidden, I], activation code) if this is a bias-free gated
         feed-forward down(act(gate(x)) * up(x)) that a block may fold into a fused kernel; None otherwise."""

@@ -510,9 +510,13 @@ class PreNormScaledBlock(Block):
         s1 = self.tensors[self.names["mixer_scale"]] if self.layer_scale else None
         if self.feed_forward is not None:
             K.norm_add_norm(stream, a, s1, plain=True, next_norm=(*self.feed_forward_norm.row_params(), h2))
-            f = self.feed_forward.forward(h2, ctx)
             s2 = self.tensors[self.names["feed_forward_scale"]] if self.layer_scale else None
-            K.norm_add_norm(stream, f, s2, plain=True, next_norm=(*nxt, h2) if nxt is not None else None)
+            # a feed-forward whose last kernel can add to the stream itself (and leave the next norm's rows) does so
+            takes = nxt is None or not nxt[2]  # (that kernel knows the norm without the mean taken off)
+            if not (takes and self.feed_forward.forward_add(h2, ctx, stream, s2,
+                                                            (nxt[0], nxt[1], h2) if nxt is not None else None)):
+                f = self.feed_forward.forward(h2, ctx)
+                K.norm_add_norm(stream, f, s2, plain=True, next_norm=(*nxt, h2) if nxt is not None else None)
         else:
             K.norm_add_norm(stream, a, s1, plain=True, next_norm=(*nxt, h2) if nxt is not None else None)
         if nxt is not None:

@@ -106,6 +106,18 @@ class RoutedExperts(FeedForward):
         return self.top * (self.I + self.H) + self.H + self.R + 1 + shared
 
     def forward(self, x, ctx):
+        return self._run(x, ctx, None)
+
+    def forward_add(self, x, ctx, stream, scale=None, next_norm=None) -> bool:
+        """stream (32-bit, in place) += scale * forward(x), the experts' weighted sum never leaving 32-bit, and
+        `next_norm` = (weight, eps, out): the RMS norm of the updated stream's rows in `out` (which may be x itself).
+        False when this part cannot (nothing has run then): the caller then adds `forward(x)` itself."""
+        if self.weight_on != "output" or stream.shape[1] * 4 > 160 * 1024:
+            return False
+        self._run(x, ctx, (stream, scale, next_norm))
+        return True
+
+    def _run(self, x, ctx, add):
         K = kernels()
         T, top, E = x.shape[0], self.top, self.E
         ws = ctx.workspace
@@ -129,8 +141,14 @@ class RoutedExperts(FeedForward):
         shared = None
         if self.shared is not None:
             shared = (self.shared.forward(x, ctx), logits[:, self.R:self.R + 1] if self.shared_gate else None)
+        passing = (choice, E, x) if self.identity else None
+        if add is not None:
+            stream, scale, next_norm = add
+            if not K.moe_combine_add_norm(rows, place, None if on_input else weight, top, stream, scale, next_norm,
+                                          passing=passing, shared=shared):
+                raise RuntimeError("the combining kernel refused a row length that had been accepted")
+            return None
         # (a buffer of its own: the shared expert's output may lie in "ffn.out")
         out = ws.tokens("moe.out", T, self.H, x.dtype)
-        K.moe_combine(rows, place, None if on_input else weight, out, top,
-                      passing=(choice, E, x) if self.identity else None, shared=shared)
+        K.moe_combine(rows, place, None if on_input else weight, out, top, passing=passing, shared=shared)
         return out
