@@ -259,7 +259,7 @@ __device__ __forceinline__ void moe_mma(float (&c)[4], const unsigned (&a)[4], u
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool GATED>
+template <bool GATED, int STAGES>
 __global__ void __launch_bounds__(MMA_THREADS)
 moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
                        const __nv_bfloat16* __restrict__ weights, long long expert_stride,
@@ -299,12 +299,12 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
   }
   __syncthreads();
   const __nv_bfloat16* W = weights + (long long)e * expert_stride;
-  unsigned char* a_s = moe_smem;                 // [2][TILE]
-  unsigned char* b_s = moe_smem + 2 * TILE;      // [2][NB][TILE]
+  unsigned char* a_s = moe_smem;                      // [STAGES][TILE]
+  unsigned char* b_s = moe_smem + STAGES * TILE;      // [STAGES][NB][TILE]
   const int ksteps = (k_dim + MMA_BK - 1) / MMA_BK;
 
   auto issue = [&](int kt) {
-    const int st = kt & 1;
+    const int st = kt % STAGES;
     const int k0 = kt * MMA_BK;
 #pragma unroll
     for (int i = 0; i < MMA_BM * 8 / MMA_THREADS; ++i) {
@@ -328,14 +328,19 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
 #pragma unroll
     for (int t = 0; t < 8; ++t) acc[g][t][0] = acc[g][t][1] = acc[g][t][2] = acc[g][t][3] = 0.f;
 
-  issue(0);
-  moe_commit();
-  for (int kt = 0; kt < ksteps; ++kt) {
-    if (kt + 1 < ksteps) issue(kt + 1);
+  // a ring of STAGES k slices: STAGES - 1 are in flight while one is multiplied (2 for steps of many rows, where
+  // the blocks of an SM hide one another's loads; 4 for steps of few rows, where a block streams its weights alone)
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {
+    if (i < ksteps) issue(i);
     moe_commit();
-    moe_wait<1>();
+  }
+  for (int kt = 0; kt < ksteps; ++kt) {
+    if (kt + STAGES - 1 < ksteps) issue(kt + STAGES - 1);
+    moe_commit();
+    moe_wait<STAGES - 1>();
     __syncthreads();
-    const unsigned char* at = a_s + (kt & 1) * TILE;
+    const unsigned char* at = a_s + (kt % STAGES) * TILE;
 #pragma unroll
     for (int kk = 0; kk < MMA_BK / 16; ++kk) {
       unsigned a[4];
@@ -345,7 +350,7 @@ moe_grouped_mma_kernel(const __nv_bfloat16* __restrict__ x, long long x_stride,
       }
 #pragma unroll
       for (int g = 0; g < NB; ++g) {
-        const unsigned char* bt = b_s + ((kt & 1) * NB + g) * TILE;
+        const unsigned char* bt = b_s + ((kt % STAGES) * NB + g) * TILE;
 #pragma unroll
         for (int t = 0; t < 8; t += 2) {
           const int mat = lane >> 3, row = t * 8 + (mat >> 1) * 8 + (lane & 7), ch = 2 * kk + (mat & 1);
@@ -582,23 +587,27 @@ extern "C" int ullm_moe_grouped_linear(int dtype, const void* x, long long x_str
       const int row_tiles = (pairs + MMA_BM - 1) / MMA_BM + experts;
       if (row_tiles > 65535) return ULLM_ERR_BAD_SIZE;
       const dim3 grid((n_out + MMA_BN - 1) / MMA_BN, row_tiles), block(MMA_THREADS);
-      const size_t smem = (size_t)2 * (1 + (gated ? 2 : 1)) * MMA_BM * MMA_BK * 2;
+      // steps of few rows: every block streams its expert's weights nearly alone, so more of them are kept in flight
+      const int stages = pairs <= 256 ? 4 : 2;
+      const size_t smem = (size_t)stages * (1 + (gated ? 2 : 1)) * MMA_BM * MMA_BK * 2;
       static int attr_set = 0;
       if (!attr_set) {  // (with the static arrays the gated form is just above the size a kernel gets unasked)
-        if (cudaFuncSetAttribute(moe_grouped_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) !=
-                cudaSuccess ||
-            cudaFuncSetAttribute(moe_grouped_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) !=
-                cudaSuccess)
+        if (cudaFuncSetAttribute(moe_grouped_mma_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(moe_grouped_mma_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(moe_grouped_mma_kernel<true, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(moe_grouped_mma_kernel<false, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 112 * 1024) != cudaSuccess)
           return ULLM_ERR_LAUNCH;
         attr_set = 1;
       }
-      if (gated)
-        return ullm_launch_kernel(moe_grouped_mma_kernel<true>, grid, block, smem, st, (const __nv_bfloat16*)x, x_stride,
-                                  (const __nv_bfloat16*)weights, expert_stride, offsets, sorted, pair_weight,
-                                  (__nv_bfloat16*)out, experts, top, rows_from_pairs, n_out, k_dim, act, limit, alpha);
-      return ullm_launch_kernel(moe_grouped_mma_kernel<false>, grid, block, smem, st, (const __nv_bfloat16*)x, x_stride,
-                                (const __nv_bfloat16*)weights, expert_stride, offsets, sorted, pair_weight,
-                                (__nv_bfloat16*)out, experts, top, rows_from_pairs, n_out, k_dim, act, limit, alpha);
+#define MMA_GO(G, S)                                                                                                  \
+  return ullm_launch_kernel(moe_grouped_mma_kernel<G, S>, grid, block, smem, st, (const __nv_bfloat16*)x, x_stride,    \
+                            (const __nv_bfloat16*)weights, expert_stride, offsets, sorted, pair_weight,               \
+                            (__nv_bfloat16*)out, experts, top, rows_from_pairs, n_out, k_dim, act, limit, alpha)
+      if (gated && stages == 4) MMA_GO(true, 4);
+      if (gated) MMA_GO(true, 2);
+      if (stages == 4) MMA_GO(false, 4);
+      MMA_GO(false, 2);
+#undef MMA_GO
     }
     return grouped_launch<__nv_bfloat16>(x, x_stride, weights, expert_stride, offsets, sorted, pair_weight, out,
                                          pairs, experts, top, rows_from_pairs, n_out, k_dim, gated, act, limit, alpha, st);
