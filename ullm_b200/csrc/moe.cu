@@ -21,7 +21,7 @@
 // finds its (expert, row tile) from the offsets, so the grid depends only on the step's size.
 #include "common.cuh"
 
-#define MOE_MAX_TOP 16
+#define MOE_MAX_TOP 32
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, long long logits_stride,
                                  const float* __restrict__ correction, int* __restrict__ choice,

@@ -48,8 +48,8 @@ class RoutedExperts(FeedForward):
             raise ValueError("a gate of the shared expert without a shared expert")
         if scores not in ("sigmoid", "softmax") or weight_on not in ("input", "output"):
             raise ValueError("scores: 'sigmoid' or 'softmax'; weight_on: 'input' or 'output'")
-        if not 0 < top <= num_experts + identity or top > 16 or num_experts + identity > 1024:
-            raise ValueError(f"top={top} of {num_experts} + {identity} experts: the kernels take top <= 16 and up to "
+        if not 0 < top <= num_experts + identity or top > 32 or num_experts + identity > 1024:
+            raise ValueError(f"top={top} of {num_experts} + {identity} experts: the kernels take top <= 32 and up to "
                              f"1024 router outputs")
         self.H, self.I, self.E, self.top = hidden_size, intermediate_size, num_experts, top
         self.activation, self.scores, self.renormalize, self.weight_on = activation, scores, bool(renormalize), weight_on
